@@ -19,6 +19,13 @@ from .llama import LlamaConfig, GGUFLLaMa, MarlinWeight  # noqa: F401
 from .block_manager import BlockManager, PrefixCache, PrefixCacheConfig, Seq, SeqGroup, AllocStatus  # noqa: F401
 from .gptq import gptq_matmul, marlin_weight_repack, marlin_permute_scales  # noqa: F401
 from .linear import QLinear  # noqa: F401
+from .state_cache import SlotPool, StateCache  # noqa: F401
+from .seq_ops import StepBatch  # noqa: F401
+from .inputs import prepare_step  # noqa: F401
+from .sampling import SamplingParams, Sampler  # noqa: F401
+from .registry import register_model, load_model  # noqa: F401
+from .gobesun import GobesunConfig, GobesunModel  # noqa: F401
+from .engine import ModelRunner, Scheduler, LLMEngine, Request  # noqa: F401
 from .moe import FusedMoe, topk_softmax, sort_expert_assignments, moe_gemm_gguf, moe_gemm_fp8  # noqa: F401
 
 __all__ = [n for n in dir() if not n.startswith("_")]

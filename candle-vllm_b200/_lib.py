@@ -34,6 +34,8 @@ SYMBOLS = [
     "b200_total_kernel_launches", "b200_allreduce_f32",
     "gptq_repack", "marlin_checkpoint_repack", "awq_repack", "marlin_4bit_f16", "marlin_4bit_bf16", "marlin_awq_4bit_f16", "marlin_awq_4bit_bf16",
     "gemm_half_q_half_alt", "b200_set_scratch",
+    "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled", "causal_conv_silu", "gated_delta_rule", "gated_rms_norm",
+    "qk_norm_rope_cache", "paged_attention_varlen",
 ]
 
 

@@ -396,6 +396,27 @@ class BlockManager:
         for s in group.seqs.values():
             self.tables[s.id].extend(self._alloc() for _ in range(self._missing_for_chunk(s, chunk)))
 
+    # -- incremental growth (ragged steps) ------------------------------------------------------------------------
+    def blocks_to_hold(self, seq_id: int, num_tokens: int) -> int:
+        """blocks that must still be allocated before the sequence's table covers ``num_tokens`` positions (exactly
+        ceil(num_tokens / block_size) in total: a ragged step learns a sequence's tokens as they arrive, so no block is opened ahead)"""
+        return max(0, -(-int(num_tokens) // self.block_size) - len(self.tables.get(seq_id, ())))
+
+    def grow_to(self, seq_id: int, num_tokens: int) -> List[int]:
+        """extend (or create) the table to cover ``num_tokens`` positions; returns the table"""
+        need = self.blocks_to_hold(seq_id, num_tokens)
+        if need > self.num_free_gpu_blocks():
+            self.evict_prefix_cache_until_free(need)
+        if need > self.num_free_gpu_blocks():
+            raise BackendError(f"out of GPU blocks: sequence {seq_id} needs {need} more, {self.num_free_gpu_blocks()} free")
+        t = self.tables.setdefault(seq_id, [])
+        t.extend(self._alloc() for _ in range(need))
+        return t
+
+    def free_table(self, seq_id: int) -> None:
+        for b in self.tables.pop(seq_id, ()):
+            self._release(b)
+
     # -- release / cache ----------------------------------------------------------------------------------------
     def free_sequence(self, s: Seq) -> None:
         for b in self.tables.pop(s.id):

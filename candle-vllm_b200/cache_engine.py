@@ -12,7 +12,7 @@ each rank owns its kv-head shard of every block.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -67,12 +67,19 @@ def turboquant_layer_shapes(mode: str, num_blocks: int, block_size: int, num_kv_
 
 
 class CacheEngine:
+    layer_shapes = None          # per-layer (kv heads, key size, value size); None = uniform layers
     def __init__(self, num_layers: int, num_kv_heads: int, head_dim: int, cache_config: CacheConfig,
                  dtype: torch.dtype = torch.bfloat16, device="cuda", num_shards: int = 1,
-                 layout: int = KvLayout.FLASH, pin_cpu: bool = True):
+                 layout: int = KvLayout.FLASH, pin_cpu: bool = True,
+                 layer_shapes: Optional[Sequence[Tuple[int, int, int]]] = None):
+        """``layer_shapes`` (optional): one (kv heads, key size, value size) per cached layer for models whose layers differ or whose
+        keys and values have different sizes; flash layout only.  Without it every layer is (num_kv_heads, head_dim, head_dim)."""
         self.num_layers = num_layers
         self.head_dim = head_dim
         self.num_kv_heads = max(num_kv_heads // max(num_shards, 1), 1)       # cache_engine.rs:306,320,335
+        self.layer_shapes = None if layer_shapes is None else [tuple(int(v) for v in s) for s in layer_shapes]
+        if self.layer_shapes is not None and (len(self.layer_shapes) != num_layers or layout != KvLayout.FLASH):
+            raise BackendError("CacheEngine: layer_shapes needs one entry per layer and the flash layout")
         self.cfg = cache_config
         self.block_size = cache_config.block_size
         self.layout = layout
@@ -83,25 +90,31 @@ class CacheEngine:
         self.cpu_cache = self._allocate(cache_config.num_cpu_blocks, torch.device("cpu"), pin_cpu) if self.cpu_swap_enabled else []
 
     # shapes: cache_engine.rs:298-341
-    def key_block_shape(self):
+    def key_block_shape(self, layer: int = 0):
+        if self.layer_shapes is not None:
+            g, dk, _ = self.layer_shapes[layer]
+            return (self.block_size, g, dk)
         if self.layout == KvLayout.FLASH:
             return (self.block_size, self.num_kv_heads, self.head_dim)
         x = 16 // torch.empty((), dtype=self.dtype).element_size()
         return (self.num_kv_heads, self.head_dim // x, self.block_size, x)
 
-    def value_block_shape(self):
+    def value_block_shape(self, layer: int = 0):
+        if self.layer_shapes is not None:
+            g, _, dv = self.layer_shapes[layer]
+            return (self.block_size, g, dv)
         if self.layout == KvLayout.FLASH:
             return (self.block_size, self.num_kv_heads, self.head_dim)
         return (self.num_kv_heads, self.head_dim, self.block_size)
 
     def _allocate(self, num_blocks: int, device, pin: bool) -> List[Tuple[torch.Tensor, torch.Tensor]]:
         out = []
-        for _ in range(self.num_layers):
+        for i in range(self.num_layers):
             kw = dict(dtype=self.dtype, device=device)
             if device.type == "cpu" and pin and torch.cuda.is_available():
                 kw["pin_memory"] = True
-            k = torch.zeros((num_blocks,) + self.key_block_shape(), **kw)
-            v = torch.zeros((num_blocks,) + self.value_block_shape(), **kw)
+            k = torch.zeros((num_blocks,) + self.key_block_shape(i), **kw)
+            v = torch.zeros((num_blocks,) + self.value_block_shape(i), **kw)
             out.append((k, v))
         return out
 
@@ -109,8 +122,7 @@ class CacheEngine:
         return self.gpu_cache
 
     def bytes_per_block(self) -> int:
-        k, v = self.gpu_cache[0]
-        return (k[0].numel() + v[0].numel()) * k.element_size() * self.num_layers
+        return sum((k[0].numel() + v[0].numel()) * k.element_size() for k, v in self.gpu_cache)
 
     def swap_in(self, src_to_dst: Dict[int, int]) -> int:
         if not self.cpu_swap_enabled:

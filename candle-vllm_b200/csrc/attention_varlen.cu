@@ -1,0 +1,189 @@
+// attention_varlen.cu -- softmax attention over the paged cache for ragged steps (portions of prompts beside single decoded
+// tokens in one launch), with separate key and value sizes, an f32 or bf16 cache, and a visibility rule per query:
+//     key j is seen by the query at position i  iff  j <= i, floor(j / chunk) == floor(i / chunk) when chunk > 0, and
+//     i - j < window when window > 0.
+// Chunks and windows are counted in sequence positions, so the result does not depend on where a prompt was cut.
+//
+//   qk_norm_rope_cache      from the packed f32 product [T, H dk | G dk | G dv] of a fused q|k|v projection: RMS norm over the WHOLE
+//                           q row and the whole k row (weights of that length; optional), rotation of the first rot_dims entries
+//                           of every head, entry i paired with i + rot_dims/2, by a cos/sin table [max_pos, rot_dims/2] that
+//                           already carries any frequency scaling and magnitude factor (optional), q written out in f32, k and v
+//                           written into the paged cache at slot_mapping[t] (K [nb, bs, G, dk], V [nb, bs, G, dv]).
+//   paged_attention_varlen  one warp per (token, head); keys in tiles of 32 (a lane scores one key, the tile's values are then
+//                           accumulated with lanes across the value columns), online softmax in f32.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+template <typename TC>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
+                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int32_t* __restrict__ positions,
+                          const int64_t* __restrict__ slot_mapping, float* __restrict__ q_out, TC* __restrict__ k_cache,
+                          TC* __restrict__ v_cache, int H, int G, int dk, int dv, int rot_dims, float eps) {
+    __shared__ float red[2][8];
+    const int t = blockIdx.x;
+    const float* row = qkv + (int64_t)t * ld;
+    const int nq = H * dk, nk = G * dk, nv = G * dv;
+    float sq = 0.f, sk = 0.f;
+    if (q_norm_w) {
+        for (int i = threadIdx.x; i < nq; i += 256) { const float v = row[i]; sq = fmaf(v, v, sq); }
+        for (int i = threadIdx.x; i < nk; i += 256) { const float v = row[nq + i]; sk = fmaf(v, v, sk); }
+        sq = warp_sum(sq); sk = warp_sum(sk);
+        if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = sq; red[1][threadIdx.x >> 5] = sk; }
+        __syncthreads();
+        sq = 0.f; sk = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { sq += red[0][i]; sk += red[1][i]; }
+    }
+    const float qsc = q_norm_w ? 1.0f / sqrtf(sq / (float)nq + eps) : 1.0f;
+    const float ksc = k_norm_w ? 1.0f / sqrtf(sk / (float)nk + eps) : 1.0f;
+    const int pos = positions[t];
+    const int half = rot_dims >> 1;
+    const int64_t slot = slot_mapping[t];
+    for (int e = threadIdx.x; e < nq + nk; e += 256) {
+        const bool is_q = e < nq;
+        const int idx = is_q ? e : e - nq;                     // index inside the q (or k) row
+        const float* w = is_q ? q_norm_w : k_norm_w;
+        const float sc = is_q ? qsc : ksc;
+        const int d = idx % dk;
+        float val = row[e] * sc * (w ? w[idx] : 1.0f);
+        if (cos_t && d < rot_dims) {
+            const int pd = d < half ? d + half : d - half;     // partner inside the head
+            const int pidx = idx - d + pd;
+            const float other = row[e - d + pd] * sc * (w ? w[pidx] : 1.0f);
+            const float c = cos_t[(int64_t)pos * half + (d < half ? d : d - half)];
+            const float s = sin_t[(int64_t)pos * half + (d < half ? d : d - half)];
+            val = d < half ? val * c - other * s : val * c + other * s;
+        }
+        if (is_q) q_out[(int64_t)t * nq + idx] = val;
+        else if (slot >= 0) k_cache[slot * nk + idx] = from_f32<TC>(val);
+    }
+    if (slot >= 0)
+        for (int i = threadIdx.x; i < nv; i += 256) v_cache[slot * nv + i] = from_f32<TC>(row[nq + nk + i]);
+}
+
+constexpr int kMaxVPerLane = 8;      // value size <= 256
+
+template <typename TC, typename TOut>
+__global__ void __launch_bounds__(128)
+paged_attention_varlen_kernel(const float* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
+                              const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ token_seq,
+                              const int32_t* __restrict__ positions, TOut* __restrict__ out, int64_t items, int H, int G, int dk, int dv,
+                              int block_size, float scale, int chunk, int window) {
+    extern __shared__ float qsm[];                  // [4 warps][dk]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * 4 + warp;
+    if (item >= items) return;
+    const int64_t t = item / H;
+    const int h = (int)(item - t * H);
+    const int g = h / (H / G);
+    const int pos = positions[t];
+    const int32_t* table = block_tables + (int64_t)token_seq[t] * table_width;
+    float* qs = qsm + warp * dk;
+    for (int i = lane; i < dk; i += 32) qs[i] = q[((int64_t)t * H + h) * dk + i] * scale;
+    __syncwarp();
+    int lo = 0;
+    if (chunk > 0) lo = (pos / chunk) * chunk;
+    if (window > 0 && pos - window + 1 > lo) lo = pos - window + 1;
+    float m = -INFINITY, l = 0.f;
+    float acc[kMaxVPerLane];
+#pragma unroll
+    for (int c = 0; c < kMaxVPerLane; ++c) acc[c] = 0.f;
+    for (int j0 = lo; j0 <= pos; j0 += 32) {
+        const int j = j0 + lane;
+        const bool valid = j <= pos;
+        int64_t phys = 0;
+        float s = -INFINITY;
+        if (valid) {
+            phys = (int64_t)table[j / block_size] * block_size + j % block_size;
+            const TC* kr = k_cache + (phys * G + g) * dk;
+            float d = 0.f;
+            for (int i = 0; i < dk; ++i) d = fmaf(qs[i], to_f32<TC>(kr[i]), d);
+            s = d;
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = valid ? expf(s - m_new) : 0.f;
+        const float corr = expf(m - m_new);          // m = -inf on the first tile: exp(-inf) = 0, acc and l are 0 anyway
+        l = l * corr + warp_sum(p);
+        m = m_new;
+#pragma unroll
+        for (int c = 0; c < kMaxVPerLane; ++c) acc[c] *= corr;
+        const int cnt = min(32, pos - j0 + 1);
+        for (int kk = 0; kk < cnt; ++kk) {
+            const float pk = __shfl_sync(0xffffffffu, p, kk);
+            const int64_t ph = __shfl_sync(0xffffffffu, phys, kk);
+            const TC* vr = v_cache + (ph * G + g) * dv;
+#pragma unroll
+            for (int c = 0; c < kMaxVPerLane; ++c) {
+                const int i = lane + 32 * c;
+                if (i < dv) acc[c] = fmaf(pk, to_f32<TC>(vr[i]), acc[c]);
+            }
+        }
+    }
+    const float inv = 1.0f / l;
+#pragma unroll
+    for (int c = 0; c < kMaxVPerLane; ++c) {
+        const int i = lane + 32 * c;
+        if (i < dv) out[((int64_t)t * H + h) * dv + i] = from_f32<TOut>(acc[c] * inv);
+    }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, const float* k_norm_w, const float* cos_t, const float* sin_t,
+                        int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, float* q_out, void* key_cache, void* value_cache,
+                        int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,
+                        int32_t cache_dtype, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(qkv && positions && slot_mapping && q_out && key_cache && value_cache, kErrBadArg, "qk_norm_rope_cache: null pointer");
+    B200_REQUIRE((q_norm_w == nullptr) == (k_norm_w == nullptr) && (cos_t == nullptr) == (sin_t == nullptr), kErrBadArg,
+                 "qk_norm_rope_cache: norm weights / tables come in pairs");
+    B200_REQUIRE(num_heads > 0 && num_kv_heads > 0 && dk > 0 && dv > 0 && rot_dims >= 0 && rot_dims <= dk && rot_dims % 2 == 0 &&
+                 ld >= (int64_t)num_heads * dk + (int64_t)num_kv_heads * (dk + dv) && (!cos_t || max_pos > 0),
+                 kErrBadArg, "qk_norm_rope_cache: bad sizes");
+    cudaStream_t st = as_stream(stream);
+    if (cache_dtype == B200_F32)
+        qk_norm_rope_cache_kernel<float><<<num_tokens, 256, 0, st>>>(qkv, ld, q_norm_w, k_norm_w, cos_t, sin_t, positions, slot_mapping, q_out,
+                                                                     (float*)key_cache, (float*)value_cache, num_heads, num_kv_heads, dk, dv, rot_dims, eps);
+    else if (cache_dtype == B200_BF16)
+        qk_norm_rope_cache_kernel<__nv_bfloat16><<<num_tokens, 256, 0, st>>>(qkv, ld, q_norm_w, k_norm_w, cos_t, sin_t, positions, slot_mapping, q_out,
+                                                                             (__nv_bfloat16*)key_cache, (__nv_bfloat16*)value_cache, num_heads,
+                                                                             num_kv_heads, dk, dv, rot_dims, eps);
+    else { set_error(kErrUnsupported, "qk_norm_rope_cache: cache dtype %d (f32 / bf16)", cache_dtype); return; }
+    count_launch();
+    check_launch("qk_norm_rope_cache");
+}
+
+void paged_attention_varlen(void* out, const float* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,
+                            int32_t table_width, const int32_t* token_seq, const int32_t* positions, int32_t num_tokens, int32_t num_heads,
+                            int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t block_size, float scale, int32_t chunk, int32_t window,
+                            int32_t cache_dtype, int32_t out_dtype, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(out && q && key_cache && value_cache && block_tables && token_seq && positions, kErrBadArg, "paged_attention_varlen: null pointer");
+    B200_REQUIRE(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dk > 0 && dv > 0 && block_size > 0 && table_width > 0,
+                 kErrBadArg, "paged_attention_varlen: bad sizes");
+    B200_REQUIRE(dv <= 32 * kMaxVPerLane && dk <= 2048, kErrUnsupported, "paged_attention_varlen: value size %d > %d or key size %d > 2048", dv,
+                 32 * kMaxVPerLane, dk);
+    const int64_t items = (int64_t)num_tokens * num_heads;
+    const unsigned grid = (unsigned)((items + 3) / 4);
+    const size_t smem = (size_t)4 * dk * sizeof(float);
+    cudaStream_t st = as_stream(stream);
+#define PAV(TC, TO) paged_attention_varlen_kernel<TC, TO><<<grid, 128, smem, st>>>(q, (const TC*)key_cache, (const TC*)value_cache, block_tables, \
+        table_width, token_seq, positions, (TO*)out, items, num_heads, num_kv_heads, dk, dv, block_size, scale, chunk, window)
+    if (cache_dtype == B200_F32 && out_dtype == B200_F32) PAV(float, float);
+    else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16) PAV(__nv_bfloat16, __nv_bfloat16);
+    else if (cache_dtype == B200_BF16 && out_dtype == B200_F32) PAV(__nv_bfloat16, float);
+    else { set_error(kErrUnsupported, "paged_attention_varlen: cache dtype %d / out dtype %d", cache_dtype, out_dtype); return; }
+#undef PAV
+    count_launch();
+    check_launch("paged_attention_varlen");
+}
+
+}  // extern "C"

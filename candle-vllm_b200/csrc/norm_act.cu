@@ -1,0 +1,113 @@
+// norm_act.cu -- the row-wise pieces between the matrix products of the pre+post-norm decoder family, all 32-bit inside:
+//   rms_norm_ex      out[r] = (residual[r] +) x[src(r)] / sqrt(mean(x^2) + eps) * (offset + w)   -- offset 1 for weights stored
+//                    around zero; `residual` makes it the closing norm of a sublayer (the sum stays f32, in place is fine);
+//                    `row_index` gathers the rows whose result is wanted (the logits of a step);
+//   gelu_tanh_mul    out = gelu_tanh(gate) * up from the packed [rows, 2 ff] product of a fused gate|up projection;
+//   embedding_scaled out[t] = table[ids[t]] * scale, table f32 or bf16.
+// Any row length (no vector-width rule): the rows these models use are a few hundred to a few thousand floats and every kernel
+// here is one pass over them from L2.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i];
+    __syncthreads();
+    return t;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+rms_norm_ex_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* out, const float* residual,
+                   const int32_t* __restrict__ row_index, int n, int64_t ldx, float eps, float offset) {
+    __shared__ float red[8];
+    const int row = blockIdx.x;
+    const int64_t src = row_index ? row_index[row] : row;
+    const float* xr = x + src * ldx;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    const float tot = block_sum_256(ss, red);
+    const float sc = 1.0f / sqrtf(tot / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += 256) {
+        float v = xr[i] * sc * (offset + w[i]);
+        if (residual) v += residual[(int64_t)row * n + i];
+        out[(int64_t)row * n + i] = from_f32<TOut>(v);
+    }
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    const float c = 0.7978845608028654f;       // sqrt(2 / pi)
+    return 0.5f * z * (1.0f + tanhf(c * (z + 0.044715f * z * z * z)));
+}
+
+template <typename TOut>
+__global__ void gelu_tanh_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int64_t rows, int ff, int64_t ld) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * ff) return;
+    const int64_t r = i / ff;
+    const int c = (int)(i - r * ff);
+    const float g = gu[r * ld + c], u = gu[r * ld + ff + c];
+    out[i] = from_f32<TOut>(gelu_tanh_f(g) * u);
+}
+
+template <typename TTab>
+__global__ void embedding_scaled_kernel(const TTab* __restrict__ table, const int32_t* __restrict__ ids, float* __restrict__ out, int dim,
+                                        int vocab, float scale) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) out[(int64_t)t * dim + i] = to_f32<TTab>(table[(int64_t)id * dim + i]) * scale;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+void rms_norm_ex(const float* x, const float* weight, void* out, const float* residual, const int32_t* row_index, int32_t rows, int32_t n,
+                 int64_t ldx, float eps, float weight_offset, int32_t out_dtype, int64_t stream) {
+    if (rows == 0) return;
+    B200_REQUIRE(x && weight && out && rows > 0 && n > 0 && ldx >= n, kErrBadArg, "rms_norm_ex: bad arguments");
+    B200_REQUIRE(!residual || out_dtype == B200_F32, kErrUnsupported, "rms_norm_ex: the residual sum is f32");
+    cudaStream_t st = as_stream(stream);
+    if (out_dtype == B200_F32) rms_norm_ex_kernel<float><<<rows, 256, 0, st>>>(x, weight, (float*)out, residual, row_index, n, ldx, eps, weight_offset);
+    else if (out_dtype == B200_BF16) rms_norm_ex_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(x, weight, (__nv_bfloat16*)out, residual, row_index, n, ldx, eps, weight_offset);
+    else { set_error(kErrUnsupported, "rms_norm_ex: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    check_launch("rms_norm_ex");
+}
+
+void gelu_tanh_mul(const float* gate_up, void* out, int64_t rows, int32_t ff, int64_t ld, int32_t out_dtype, int64_t stream) {
+    if (rows == 0 || ff == 0) return;
+    B200_REQUIRE(gate_up && out && rows > 0 && ff > 0 && ld >= 2 * (int64_t)ff, kErrBadArg, "gelu_tanh_mul: bad arguments");
+    const int64_t total = rows * ff;
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    cudaStream_t st = as_stream(stream);
+    if (out_dtype == B200_F32) gelu_tanh_mul_kernel<float><<<grid, 256, 0, st>>>(gate_up, (float*)out, rows, ff, ld);
+    else if (out_dtype == B200_BF16) gelu_tanh_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(gate_up, (__nv_bfloat16*)out, rows, ff, ld);
+    else { set_error(kErrUnsupported, "gelu_tanh_mul: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    check_launch("gelu_tanh_mul");
+}
+
+void embedding_scaled(const void* table, const int32_t* ids, float* out, int32_t num_tokens, int32_t dim, int32_t vocab, float scale,
+                      int32_t table_dtype, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(table && ids && out && dim > 0 && vocab > 0, kErrBadArg, "embedding_scaled: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    if (table_dtype == B200_F32) embedding_scaled_kernel<float><<<num_tokens, 128, 0, st>>>((const float*)table, ids, out, dim, vocab, scale);
+    else if (table_dtype == B200_BF16) embedding_scaled_kernel<__nv_bfloat16><<<num_tokens, 128, 0, st>>>((const __nv_bfloat16*)table, ids, out, dim, vocab, scale);
+    else { set_error(kErrUnsupported, "embedding_scaled: table dtype %d (f32 / bf16)", table_dtype); return; }
+    count_launch();
+    check_launch("embedding_scaled");
+}
+
+}  // extern "C"

@@ -1,0 +1,193 @@
+"""Serving loop for ragged-step models: the step function (``ModelRunner.execute``), the request scheduler with chunked prefill and
+continuous batching, and ``LLMEngine.generate``.  Roles follow the reference's ``LLMEngine`` + ``Scheduler``
+(/root/reference/src/openai/pipelines/llm_engine.rs, /root/reference/src/scheduler/mod.rs): waiting -> running queues, a token budget per
+step, blocks from ``BlockManager``, recurrent-state slots from ``StateCache``; unlike the reference a step may carry prompt portions
+and decoded tokens together.
+
+``ModelRunner`` is the only place that touches caches: it owns the ``CacheEngine`` (paged K / V per attention run), the ``StateCache``
+(f32 state per recurrent run) and the ``BlockManager``; callers name sequences by id.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ._lib import BackendError
+from .block_manager import BlockManager
+from .cache_engine import CacheConfig, CacheEngine
+from .inputs import prepare_step
+from .sampling import Sampler, SamplingParams
+from .seq_ops import StepBatch
+from .state_cache import StateCache
+
+
+class ModelRunner:
+    def __init__(self, model, num_blocks: int, num_slots: int, block_size: int = 64):
+        self.model, self.block_size = model, block_size
+        plan = model.cache_plan()
+        kv = plan["kv_layers"]
+        self.cache = CacheEngine(len(kv), 0, 0, CacheConfig(block_size, num_blocks), dtype=model.dtype, device=model.device, layer_shapes=kv) if kv else None
+        self.state = StateCache(plan["state_layers"], num_slots, device=model.device)
+        self.blocks = BlockManager(block_size, num_blocks, 0)
+        self.lengths: Dict[int, int] = {}          # tokens of each live sequence already in cache / state
+
+    # -- sequence lifetime -------------------------------------------------------------------------------------------
+    def can_admit(self, num_tokens: int, reserved_blocks: int = 0) -> bool:
+        return self.state.pool.num_free() > 0 and -(-num_tokens // self.block_size) <= self.blocks.num_free_gpu_blocks() - reserved_blocks
+
+    def admit(self, seq_id: int) -> None:
+        if seq_id in self.lengths:
+            raise BackendError(f"sequence {seq_id} is already live")
+        self.state.pool.acquire(seq_id)
+        self.lengths[seq_id] = 0
+
+    def release(self, seq_id: int) -> None:
+        self.blocks.free_table(seq_id)
+        self.state.pool.release(seq_id)
+        self.lengths.pop(seq_id, None)
+
+    # -- the step ----------------------------------------------------------------------------------------------------
+    def execute(self, entries: Sequence[dict], hidden_trace: Optional[list] = None) -> Optional[torch.Tensor]:
+        """entries: dict(seq_id, tokens, want) -- the next tokens of live sequences.  Runs them as ONE batch from the cache and state
+        earlier steps left; returns f32 logits [sum(len(want)), vocab] on the device in entry order (None if nothing is wanted)."""
+        if not entries:
+            return None
+        rows = []
+        for e in entries:
+            sid, toks = e["seq_id"], e["tokens"]
+            if sid not in self.lengths:
+                raise BackendError(f"sequence {sid} was not admitted")
+            start = self.lengths[sid]
+            table = self.blocks.grow_to(sid, start + len(toks))
+            rows.append(dict(tokens=toks, start=start, block_table=table, state_slot=self.state.pool.slot_of(sid), want=e.get("want", ())))
+        batch = StepBatch.from_host(prepare_step(rows, self.block_size), self.model.device)
+        logits = self.model.forward(batch, self.cache.gpu_cache if self.cache else [], self.state.tensors, hidden_trace)
+        for e in entries:
+            self.lengths[e["seq_id"]] += len(e["tokens"])
+        return logits
+
+
+@dataclass
+class Request:
+    id: int
+    prompt: List[int]
+    params: SamplingParams
+    output: List[int] = field(default_factory=list)
+    computed: int = 0                  # tokens already run through the model
+    finished: bool = False
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+
+class Scheduler:
+    """FCFS continuous batching with chunked prefill.  A request is admitted when a state slot is free and the blocks for its prompt plus
+    its ``max_tokens`` fit beside what the running requests have reserved, so a running request never has to be preempted."""
+
+    def __init__(self, runner: ModelRunner, max_batch_tokens: int = 2048, max_num_seqs: int = 4, prefill_chunk: int = 512):
+        self.runner, self.max_batch_tokens, self.max_num_seqs, self.prefill_chunk = runner, max_batch_tokens, max_num_seqs, prefill_chunk
+        self.waiting: "deque[Request]" = deque()
+        self.running: List[Request] = []
+
+    def _blocks_for(self, r: Request) -> int:
+        return -(-(len(r.prompt) + r.params.max_tokens) // self.runner.block_size)
+
+    def _reserved(self) -> int:
+        held = lambda r: len(self.runner.blocks.tables.get(r.id, ()))
+        return sum(max(0, self._blocks_for(r) - held(r)) for r in self.running)
+
+    def add(self, r: Request) -> None:
+        if self._blocks_for(r) > self.runner.blocks.num_gpu_blocks:
+            raise BackendError(f"request {r.id} needs {self._blocks_for(r)} blocks, the pool has {self.runner.blocks.num_gpu_blocks}")
+        self.waiting.append(r)
+
+    def schedule(self) -> List[dict]:
+        """-> entries for ModelRunner.execute (each also carries its Request under 'request')"""
+        while self.waiting and len(self.running) < self.max_num_seqs:
+            r = self.waiting[0]
+            if self.runner.state.pool.num_free() == 0 or self._blocks_for(r) > self.runner.blocks.num_free_gpu_blocks() - self._reserved():
+                break
+            self.waiting.popleft()
+            self.runner.admit(r.id)
+            self.running.append(r)
+        budget, entries = self.max_batch_tokens, []
+        for r in self.running:                       # decodes first: one token each
+            if r.computed >= len(r.prompt) and budget > 0:
+                entries.append(dict(seq_id=r.id, tokens=[r.tokens[-1]], want=[0], request=r))
+                budget -= 1
+        for r in self.running:                       # then prompt portions
+            if r.computed < len(r.prompt) and budget > 0:
+                n = min(len(r.prompt) - r.computed, self.prefill_chunk, budget)
+                toks = r.prompt[r.computed:r.computed + n]
+                last = r.computed + n == len(r.prompt)
+                entries.append(dict(seq_id=r.id, tokens=toks, want=[n - 1] if last else [], request=r))
+                budget -= n
+        return entries
+
+    def finish(self, r: Request) -> None:
+        r.finished = True
+        self.running.remove(r)
+        self.runner.release(r.id)
+
+
+class LLMEngine:
+    def __init__(self, model, num_blocks: int = 256, max_num_seqs: int = 4, block_size: int = 64, max_batch_tokens: int = 2048,
+                 prefill_chunk: int = 512):
+        self.model = model
+        self.runner = ModelRunner(model, num_blocks, max_num_seqs, block_size)
+        self.scheduler = Scheduler(self.runner, max_batch_tokens, max_num_seqs, prefill_chunk)
+        self.sampler = Sampler()
+        self._next_id = 0
+        self.steps = 0
+
+    @classmethod
+    def from_pretrained(cls, path: str, dtype: torch.dtype = torch.bfloat16, max_model_len: int = 4096, **kw) -> "LLMEngine":
+        from .registry import load_model
+        block_size = kw.get("block_size", 64)
+        return cls(load_model(path, dtype=dtype, block_size=block_size, max_pos=max_model_len), **kw)
+
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> Request:
+        if len(prompt) == 0:
+            raise BackendError("empty prompt")
+        r = Request(self._next_id, [int(t) for t in prompt], params or SamplingParams())
+        self._next_id += 1
+        self.scheduler.add(r)
+        return r
+
+    def has_work(self) -> bool:
+        return bool(self.scheduler.waiting or self.scheduler.running)
+
+    def step(self) -> List[Request]:
+        """one scheduled batch through the model; returns the requests that finished in it"""
+        entries = self.scheduler.schedule()
+        if not entries:
+            if self.scheduler.waiting:
+                raise BackendError("scheduler stalled: a waiting request cannot be admitted and nothing is running")
+            return []
+        logits = self.runner.execute(entries)
+        self.steps += 1
+        done = []
+        sampled = [e for e in entries if e["want"]]
+        for e in entries:
+            e["request"].computed += len(e["tokens"])
+        if sampled:
+            toks = self.sampler.sample(logits, [e["request"].params for e in sampled], [e["request"].id for e in sampled])
+            for e, t in zip(sampled, toks):
+                r = e["request"]
+                r.output.append(t)
+                if len(r.output) >= r.params.max_tokens or t in r.params.stop_token_ids:
+                    self.scheduler.finish(r)
+                    self.sampler.forget(r.id)
+                    done.append(r)
+        return done
+
+    def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[List[int]]:
+        ps = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        reqs = [self.add_request(p, q) for p, q in zip(prompts, ps)]
+        while self.has_work():
+            self.step()
+        return [r.output for r in reqs]

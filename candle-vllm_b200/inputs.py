@@ -97,6 +97,36 @@ def prepare_prompt(prompts: Sequence[Sequence[int]], block_tables: Sequence[Sequ
                 block_tables=_pad_tables(tabs), max_context_len=max_k)
 
 
+def prepare_step(entries: Sequence[dict], block_size: int) -> dict:
+    """Metadata of one ragged step: portions of prompts and single decoded tokens side by side (the reference mixes them only across
+    steps, inputs.rs:90-374 / :376-454; the layout below is the union of both).  Each entry is a dict with ``tokens`` (the ids this step
+    brings for the sequence), ``start`` (position of the first of them), ``block_table`` (covering start + len(tokens) positions),
+    ``state_slot`` (recurrent-state slot, -1 if the model has none) and ``want`` (indices into ``tokens`` whose logits are asked for).
+    Rows are laid out entry after entry."""
+    tokens, positions, token_seq, slots, want_rows = [], [], [], [], []
+    cu, seq_slots, seq_start, tabs = [0], [], [], []
+    for b, e in enumerate(entries):
+        toks, start, table = e["tokens"], int(e["start"]), e["block_table"]
+        if len(toks) == 0:
+            raise BackendError("prepare_step: an entry without tokens")
+        base = cu[-1]
+        for i, tok in enumerate(toks):
+            p = start + i
+            tokens.append(int(tok)); positions.append(p); token_seq.append(b)
+            slots.append(_slot(table, p, block_size, "step"))
+        for w in e.get("want", ()):
+            if not 0 <= int(w) < len(toks):
+                raise BackendError(f"prepare_step: wanted index {w} outside the entry's {len(toks)} tokens")
+            want_rows.append(base + int(w))
+        cu.append(base + len(toks))
+        seq_slots.append(int(e.get("state_slot", -1))); seq_start.append(start)
+        tabs.append(list(table[:used_blocks_for_len(start + len(toks), block_size, len(table))]))
+    return dict(tokens=np.asarray(tokens, np.int32), positions=np.asarray(positions, np.int32), token_seq=np.asarray(token_seq, np.int32),
+                slot_mapping=np.asarray(slots, np.int64), cu_seqlens=np.asarray(cu, np.int32), seq_slots=np.asarray(seq_slots, np.int32),
+                seq_start=np.asarray(seq_start, np.int32), block_tables=_pad_tables(tabs), want_rows=np.asarray(want_rows, np.int32),
+                max_position=max(positions) if positions else 0)
+
+
 def flashinfer_csr(lens: Sequence[int], block_tables: Sequence[Sequence[int]], block_size: int) -> dict:
     """The CSR page tables the reference builds for its flashinfer backend (inputs.rs:477-531): ``indptr`` [B + 1], ``indices`` (the used
     blocks of every sequence, back to back), ``last_len`` = (len - 1) % block_size + 1 (0 for an empty sequence) and the derived

@@ -1,0 +1,129 @@
+"""Sequence mixers and feed-forward blocks for ragged-step models, each a thin object that owns its (fused) weights and calls the
+kernels of ``seq_ops``.  Sizes and constants are constructor arguments so that any decoder built from these parts can use them:
+
+  GatedDeltaMixer      short causal convolution + SiLU on q / k / v, unit-norm q and k, gated delta rule over an f32 state, per-head
+                       RMS norm times a SiLU gate, output projection (csrc/gated_delta.cu)
+  PagedAttentionMixer  grouped-query attention over the paged cache with optional whole-row q / k RMS norm, partial rotary with
+                       optional YaRN scaling, and a chunk and / or sliding-window mask (csrc/attention_varlen.cu)
+  GatedMlp             down(act(gate x) * (up x)) with the tanh GELU (csrc/norm_act.cu)
+
+Activations that feed a matrix product are of the model's compute dtype (bf16 or f32); products come back in f32 and everything
+between them (norms, convolution, recurrence, softmax) is 32-bit.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ._lib import BackendError
+from . import seq_ops as ops
+from .seq_ops import StepBatch
+
+
+def yarn_rotary_tables(dims: int, base: float, max_pos: int, scaling: Optional[dict] = None, device="cuda") -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin f32 [max_pos, dims/2] for the rotate-half layout, angles computed in float64.  ``scaling`` = dict(factor, original, fast,
+    slow) applies YaRN: with c(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(c(fast)), 0), hi = min(ceil(c(slow)),
+    dims - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), frequency i becomes f_i / factor * r_i + f_i * (1 - r_i), and cos /
+    sin are multiplied by 0.1 * ln(factor) + 1."""
+    half = dims // 2
+    i = torch.arange(half, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    mag = 1.0
+    if scaling:
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+        corr = lambda turns: dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+        lo = max(math.floor(corr(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(corr(float(scaling["slow"]))), dims - 1)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        f = f / factor * ramp + f * (1.0 - ramp)
+        mag = 0.1 * math.log(factor) + 1.0
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * f[None, :]
+    return (torch.cos(ang) * mag).float().to(device), (torch.sin(ang) * mag).float().to(device)
+
+
+class GatedDeltaMixer:
+    """weights: q, k [G dk, D], v, g [H dv, D], b, a [H, D], o [D, H dv] (compute dtype); q.conv / k.conv / v.conv [channels, taps], A_log,
+    dt_bias [H], norm [dv].  One fused projection q|k|v|g|b|a per step."""
+    kind = "state"
+
+    def __init__(self, w: Dict[str, torch.Tensor], heads: int, kv_heads: int, dk: int, dv: int, taps: int, eps: float, dtype: torch.dtype):
+        if heads % kv_heads:
+            raise BackendError("GatedDeltaMixer: heads must be a multiple of kv_heads")
+        self.H, self.G, self.dk, self.dv, self.taps, self.eps, self.dtype = heads, kv_heads, dk, dv, taps, eps, dtype
+        self.C = 2 * kv_heads * dk + heads * dv
+        self.w_in = torch.cat([w["q"], w["k"], w["v"], w["g"], w["b"], w["a"]], 0).to(dtype).contiguous()
+        self.off_g = self.C
+        self.off_b = self.C + heads * dv
+        self.off_a = self.off_b + heads
+        self.conv = torch.cat([w["q.conv"], w["k.conv"], w["v.conv"]], 0).float().contiguous()
+        if self.conv.shape != (self.C, taps):
+            raise BackendError(f"GatedDeltaMixer: convolution taps {tuple(self.conv.shape)} != {(self.C, taps)}")
+        self.A_log, self.dt_bias, self.norm = w["A_log"].float().contiguous(), w["dt_bias"].float().contiguous(), w["norm"].float().contiguous()
+        self.w_o = w["o"].to(dtype).contiguous()
+
+    def state_shapes(self):
+        return ((self.taps - 1, self.C), (self.H, self.dk, self.dv))
+
+    def forward(self, h: torch.Tensor, batch: StepBatch, cache) -> torch.Tensor:
+        conv_state, S = cache
+        proj = ops.linear(h, self.w_in)
+        y = ops.causal_conv_silu(proj[:, :self.C], self.conv, conv_state, batch)
+        o = ops.gated_delta_rule(y, proj, self.off_b, self.off_a, self.A_log, self.dt_bias, S, batch, self.H, self.G, self.dk, self.dv)
+        z = ops.gated_rms_norm(o, proj[:, self.off_g:], self.norm, self.H, self.dv, self.eps, self.dtype)
+        return ops.linear(z, self.w_o)
+
+
+class PagedAttentionMixer:
+    """weights: q [H dk, D], k [G dk, D], v [G dv, D], o [D, H dv]; optional q.norm [H dk], k.norm [G dk] (plain weights, RMS over the whole
+    row).  rot = dict(dims, base, scaling) or None; chunk / window = 0 for none."""
+    kind = "kv"
+
+    def __init__(self, w: Dict[str, torch.Tensor], heads: int, kv_heads: int, dk: int, dv: int, scale: float, eps: float, dtype: torch.dtype,
+                 rot: Optional[dict] = None, chunk: int = 0, window: int = 0, block_size: int = 64, max_pos: int = 4096):
+        if heads % kv_heads:
+            raise BackendError("PagedAttentionMixer: heads must be a multiple of kv_heads")
+        self.H, self.G, self.dk, self.dv, self.scale, self.eps, self.dtype = heads, kv_heads, dk, dv, float(scale), eps, dtype
+        self.chunk, self.window, self.block_size, self.rot = int(chunk), int(window), block_size, rot
+        self.w_in = torch.cat([w["q"], w["k"], w["v"]], 0).to(dtype).contiguous()
+        self.q_norm = w["q.norm"].float().contiguous() if "q.norm" in w else None
+        self.k_norm = w["k.norm"].float().contiguous() if "k.norm" in w else None
+        self.w_o = w["o"].to(dtype).contiguous()
+        self.rot_dims = int(rot["dims"]) if rot else 0
+        if self.rot_dims % 2 or self.rot_dims > dk:
+            raise BackendError(f"PagedAttentionMixer: {self.rot_dims} rotary dims do not fit a head of {dk}")
+        self.cos = self.sin = None
+        self._device = self.w_in.device
+        if rot:
+            self.ensure_positions(max_pos)
+
+    def ensure_positions(self, max_pos: int) -> None:
+        if self.rot and (self.cos is None or self.cos.shape[0] < max_pos):
+            self.cos, self.sin = yarn_rotary_tables(self.rot_dims, float(self.rot["base"]), max_pos, self.rot.get("scaling"), self._device)
+
+    def cache_shape(self):
+        return (self.G, self.dk, self.dv)
+
+    def forward(self, h: torch.Tensor, batch: StepBatch, cache) -> torch.Tensor:
+        k_cache, v_cache = cache
+        if self.rot and batch.max_position >= self.cos.shape[0]:
+            self.ensure_positions(max(2 * self.cos.shape[0], batch.max_position + 1))
+        proj = ops.linear(h, self.w_in)
+        q = ops.qk_norm_rope_cache(proj, self.q_norm, self.k_norm, self.cos, self.sin, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dv,
+                                   self.rot_dims, self.eps)
+        a = ops.paged_attention_varlen(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.dv, self.block_size, self.scale, self.chunk,
+                                       self.window, self.dtype)
+        return ops.linear(a, self.w_o)
+
+
+class GatedMlp:
+    """down(gelu_tanh(gate x) * (up x)); gate, up [ff, D], down [D, ff]."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], dtype: torch.dtype):
+        self.dtype = dtype
+        self.w_in = torch.cat([w["gate"], w["up"]], 0).to(dtype).contiguous()
+        self.w_down = w["down"].to(dtype).contiguous()
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return ops.linear(ops.gelu_tanh_mul(ops.linear(h, self.w_in), self.dtype), self.w_down)

@@ -1,0 +1,45 @@
+"""Model registry: ``config.json`` -> model class, the way the reference picks a pipeline from the ``architectures`` entry of a
+checkpoint (/root/reference/src/openai/pipelines/pipeline.rs, ``get_arch_cfg``).  A model class offers
+``from_pretrained(path, dtype=..., block_size=..., max_pos=...)``, ``cache_plan()`` and ``forward(batch, kv_cache, state_cache)``."""
+from __future__ import annotations
+
+import json
+import os
+from typing import Callable, Dict
+
+from ._lib import BackendError
+
+_REGISTRY: Dict[str, Callable] = {}
+
+
+def register_model(architecture: str, loader: Callable) -> None:
+    _REGISTRY[architecture] = loader
+
+
+def architecture_of(config: dict) -> str:
+    if "architecture" in config:
+        return str(config["architecture"])
+    archs = config.get("architectures")
+    if archs:
+        return str(archs[0])
+    raise BackendError("config.json names no architecture")
+
+
+def registered() -> list:
+    return sorted(_REGISTRY)
+
+
+def load_model(path: str, **kw):
+    with open(os.path.join(path, "config.json")) as f:
+        arch = architecture_of(json.load(f))
+    if arch not in _REGISTRY:
+        raise BackendError(f"no model registered for architecture {arch!r} (have: {', '.join(registered())})")
+    return _REGISTRY[arch](path, **kw)
+
+
+def _gobesun(path, **kw):
+    from .gobesun import GobesunModel
+    return GobesunModel.from_pretrained(path, **kw)
+
+
+register_model("Gobesun", _gobesun)

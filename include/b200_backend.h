@@ -400,6 +400,57 @@ int64_t b200_llama_kernel_launches(b200_llama* m);    /* kernels launched by thi
 void b200_llama_read_next_tokens(b200_llama* m, int32_t* host, int32_t n, int64_t stream);
 void b200_llama_read_logits(b200_llama* m, float* host, int32_t n, int64_t stream);
 
+/* ---- pre+post-norm decoder family with recurrent and chunk-masked mixers (models/gobesun) ---------------------------------------
+ * A ragged step carries `num_seqs` entries; entry b owns rows cu_seqlens[b] .. cu_seqlens[b+1] of the flat token arrays, continues the
+ * sequence whose recurrent state lives in slot seq_slots[b], and starts at sequence position seq_start[b] (0 = a new sequence: the slot's
+ * old contents are ignored).  token_seq[t] = entry of row t, positions[t] = its sequence position.  All of this is i32 on the device.
+ *
+ * linear_f32out: out[m, n] (f32, row pitch ldy) = x[m, k] (row pitch ldx) . weight[n, k]^T; x and weight of `dtype`: B200_F32 runs a true
+ *   32-bit SIMT product (no reduced-precision tensor mode), B200_BF16 the tcgen05 kernel with an f32 epilogue when k % 8 == 0, ldx % 8 == 0
+ *   and the bases are 16-byte aligned, a shape-generic kernel otherwise.
+ * rms_norm_ex: out[r] = (residual[r] +) x[src] / sqrt(mean(x[src]^2) + eps) * (weight_offset + weight), src = row_index ? row_index[r] : r;
+ *   residual (optional, f32 [rows, n]; may alias out) needs out_dtype F32.  out_dtype F32 / BF16, any n.
+ * gelu_tanh_mul: out[r, c] = gelu_tanh(gate_up[r, c]) * gate_up[r, ff + c] (row pitch ld >= 2 ff).
+ * embedding_scaled: out[t] = table[ids[t]] * scale, table f32 / bf16 [vocab, dim]. */
+void linear_f32out(const void* x, const void* weight, float* out, int32_t m, int32_t n, int32_t k, int64_t ldx, int64_t ldy, int32_t dtype,
+                   int64_t stream);
+void rms_norm_ex(const float* x, const float* weight, void* out, const float* residual, const int32_t* row_index, int32_t rows, int32_t n,
+                 int64_t ldx, float eps, float weight_offset, int32_t out_dtype, int64_t stream);
+void gelu_tanh_mul(const float* gate_up, void* out, int64_t rows, int32_t ff, int64_t ld, int32_t out_dtype, int64_t stream);
+void embedding_scaled(const void* table, const int32_t* ids, float* out, int32_t num_tokens, int32_t dim, int32_t vocab, float scale,
+                      int32_t table_dtype, int64_t stream);
+/* causal_conv_silu: y[t, c] (f32 [T, channels]) = silu(sum_d taps[c, K-1-d] * x[t-d, c]) per channel over time (taps f32 [channels, K], the last
+ *   column multiplies the current token); rows before the portion come from conv_state f32 [slots, K-1, channels] (the sequence's last K-1
+ *   inputs), which is then rolled forward over the portion.
+ * gated_delta_rule: qkv f32 [T, G dk | G dk | H dv] (the conv output), b and a = columns off_b + h / off_a + h of `proj` (row pitch ld_proj);
+ *   per head, state S f32 [slots, H, dk, dv]: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, q and k unit vectors (eps 1e-6,
+ *   q also times dk^-1/2), beta = sigmoid(b), g = exp(-exp(A_log[h]) * softplus(a + dt_bias[h])).  out f32 [T, H dv].  dk <= 256.
+ * gated_rms_norm: out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[dv] * silu(gate[t, h, :]) (gate row pitch ld_gate). */
+void causal_conv_silu(const float* x, int64_t ldx, const float* taps, float* conv_state, float* y, const int32_t* token_seq,
+                      const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens, int32_t num_seqs,
+                      int32_t channels, int32_t num_taps, int64_t stream);
+void gated_delta_rule(const float* qkv, const float* proj, int64_t ld_proj, int32_t off_b, int32_t off_a, const float* A_log,
+                      const float* dt_bias, float* state, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots,
+                      const int32_t* seq_start, int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv,
+                      int64_t stream);
+void gated_rms_norm(const float* o, const float* gate, int64_t ld_gate, const float* weight, void* out, int32_t num_tokens, int32_t num_heads,
+                    int32_t dv, float eps, int32_t out_dtype, int64_t stream);
+/* qk_norm_rope_cache: qkv f32 [T, H dk | G dk | G dv] (row pitch ld) -> optional RMS norm over the whole q row and the whole k row (weights
+ *   f32 [H dk], [G dk]), optional rotation of the first rot_dims entries of each head (entry i with i + rot_dims/2) by cos / sin f32
+ *   [max_pos, rot_dims/2], q_out f32 [T, H dk], K / V written at slot_mapping[t] (negative = skip) into caches [nb, bs, G, dk] / [nb, bs, G, dv]
+ *   of cache_dtype F32 / BF16.
+ * paged_attention_varlen: out[t, h, :] = softmax over the visible keys of (q[t, h] . k_j) * scale times v_j; key j of the token's sequence
+ *   (block_tables i32 [num_seqs, table_width], row token_seq[t]) is visible to position i = positions[t] iff j <= i, j / chunk == i / chunk
+ *   (chunk > 0) and i - j < window (window > 0).  dv <= 256.  out_dtype F32 / BF16. */
+void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, const float* k_norm_w, const float* cos_t, const float* sin_t,
+                        int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, float* q_out, void* key_cache, void* value_cache,
+                        int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,
+                        int32_t cache_dtype, int64_t stream);
+void paged_attention_varlen(void* out, const float* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,
+                            int32_t table_width, const int32_t* token_seq, const int32_t* positions, int32_t num_tokens, int32_t num_heads,
+                            int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t block_size, float scale, int32_t chunk, int32_t window,
+                            int32_t cache_dtype, int32_t out_dtype, int64_t stream);
+
 /* library-wide count of kernels launched by this library (evidence for bench.py's gpu_launches) */
 long long b200_total_kernel_launches(void);
 /* NCCL all-reduce(sum) in place on f32, on the caller's communicator (tensor-parallel residual path,
