@@ -13,6 +13,8 @@ import sys
 
 def _generate(argv) -> int:
     import torch
+    from ._lib import ensure_built
+    ensure_built("ragged")
     from .engine import LLMEngine
     from .sampling import SamplingParams
     ap = argparse.ArgumentParser(prog="generate")

@@ -39,6 +39,30 @@ SYMBOLS = [
 ]
 
 
+# what a library built from one source group (build.GROUPS) exports
+GROUP_SYMBOLS = {
+    "ragged": ["b200_abi_version", "b200_last_error", "b200_last_error_message", "b200_device_sm_count", "b200_device_cc",
+               "b200_total_kernel_launches", "linear_16bit", "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled",
+               "causal_conv_silu", "gated_delta_rule", "gated_rms_norm", "qk_norm_rope_cache", "paged_attention_varlen", "argmax_f32",
+               "rms_norm", "cast"],
+}
+_RESTYPES = {"b200_last_error_message": C.c_char_p, "paged_attention_decode_workspace_bytes": C.c_size_t, "qmatmul_workspace_bytes": C.c_size_t,
+             "moe_gemm_workspace_bytes": C.c_size_t, "moe_gemm_fp8_workspace_bytes": C.c_size_t, "mla_paged_decode_workspace_bytes": C.c_size_t,
+             "b200_llama_create": C.c_void_p, "b200_llama_peer_inbox_bytes": C.c_size_t, "b200_ipc_alloc": C.c_void_p, "b200_ipc_open": C.c_void_p,
+             "b200_llama_logits": C.c_void_p, "b200_llama_next_tokens": C.c_void_p, "b200_llama_kernel_launches": C.c_int64,
+             "b200_total_kernel_launches": C.c_longlong}
+
+
+def _open(path: str, symbols) -> C.CDLL:
+    L = C.CDLL(path)
+    for name in symbols:
+        getattr(L, name)            # AttributeError if the library lacks a declared symbol
+    for name, rt in _RESTYPES.items():
+        if name in symbols:
+            getattr(L, name).restype = rt
+    return L
+
+
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
@@ -46,25 +70,24 @@ def lib() -> C.CDLL:
             raise BackendError(
                 f"{_SO} not found: build it with `python candle-vllm_b200/build.py` "
                 "(nvcc, sm_100a). There is no CPU fallback.")
-        L = C.CDLL(_SO)
-        L.b200_last_error_message.restype = C.c_char_p
-        L.paged_attention_decode_workspace_bytes.restype = C.c_size_t
-        L.qmatmul_workspace_bytes.restype = C.c_size_t
-        L.moe_gemm_workspace_bytes.restype = C.c_size_t
-        L.moe_gemm_fp8_workspace_bytes.restype = C.c_size_t
-        L.mla_paged_decode_workspace_bytes.restype = C.c_size_t
-        L.b200_llama_create.restype = C.c_void_p
-        L.b200_llama_peer_inbox_bytes.restype = C.c_size_t
-        L.b200_ipc_alloc.restype = C.c_void_p
-        L.b200_ipc_open.restype = C.c_void_p
-        L.b200_llama_logits.restype = C.c_void_p
-        L.b200_llama_next_tokens.restype = C.c_void_p
-        L.b200_llama_kernel_launches.restype = C.c_int64
-        L.b200_total_kernel_launches.restype = C.c_longlong
-        for name in SYMBOLS:
-            getattr(L, name)        # AttributeError if the library lacks a declared symbol
-        _lib = L
+        _lib = _open(_SO, SYMBOLS)
     return _lib
+
+
+def ensure_built(group: str) -> C.CDLL:
+    """For programs that start from a source-only checkout: use the full library when it is there, otherwise compile (once) and load the
+    library of ``group`` alone -- the kernels one model family needs."""
+    global _lib
+    if _lib is None and not os.path.exists(_SO):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("b200_build", os.path.join(_HERE, "build.py"))
+        b = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(b)
+        path = b.so_path(group)
+        if not os.path.exists(path):
+            b.build(group=group)
+        _lib = _open(path, GROUP_SYMBOLS[group])
+    return lib()
 
 
 def check(what: str = "") -> None:

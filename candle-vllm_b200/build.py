@@ -31,9 +31,22 @@ def _newer(target: str, deps) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+# Source groups that link into a library of their own: what one model family needs, so that a first start from a source-only checkout
+# compiles that and nothing else.  "ragged" = the ragged-step decoders (seq_ops.py): error state, both linear kernels, norms /
+# activations, recurrent and attention mixers, argmax.
+GROUPS = {"ragged": ["lib", "linear_generic", "dense_gemm", "norm_act", "gated_delta", "attention_varlen", "elementwise"]}
+
+
+def so_path(group=None) -> str:
+    return SO if group is None else os.path.join(HERE, f"libb200backend.{group}.so")
+
+
+def build(force: bool = False, verbose: bool = False, group=None) -> str:
     os.makedirs(OBJ, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    if group is not None:
+        srcs = [os.path.join(CSRC, n + ".cu") for n in GROUPS[group]]
+    SO = so_path(group)
     hdrs = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
     jobs = []
     for s in srcs:
@@ -56,14 +69,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
                     raise RuntimeError(f"nvcc failed on {s}")
     objs = [os.path.join(OBJ, os.path.basename(s)[:-3] + ".o") for s in srcs]
     if force or jobs or _newer(SO, objs):
-        cmd = [NVCC, "-shared", "-o", SO, "-ccbin", CCBIN, "-gencode", "arch=compute_100a,code=sm_100a",
+        tmp = f"{SO}.{os.getpid()}.tmp"
+        cmd = [NVCC, "-shared", "-o", tmp, "-ccbin", CCBIN, "-gencode", "arch=compute_100a,code=sm_100a",
                "-cudart", "static"] + objs + ["-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+        os.replace(tmp, SO)              # a reader never sees a half-written library
     return SO
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    grp = next((a.split("=", 1)[1] for a in sys.argv if a.startswith("--group=")), None)
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, group=grp))

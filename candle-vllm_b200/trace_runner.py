@@ -30,6 +30,8 @@ def main(argv=None) -> int:
     ap.add_argument("--block-size", type=int, default=64)
     a = ap.parse_args(argv)
 
+    from ._lib import ensure_built
+    ensure_built("ragged")
     from .engine import ModelRunner
     from .registry import load_model
     torch.cuda.set_device(0)
