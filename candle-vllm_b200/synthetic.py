@@ -200,3 +200,58 @@ def random_block_tables(num_seqs: int, blocks_per_seq: int, num_blocks: int, see
     rng = np.random.default_rng(seed)
     perm = rng.permutation(num_blocks)[: num_seqs * blocks_per_seq]
     return perm.reshape(num_seqs, blocks_per_seq).tolist()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Gobesun: random checkpoints of any shape (tests and bench.py; there is no network for real ones)
+# ---------------------------------------------------------------------------------------------------------------------
+def gobesun_delta_layer(heads: int, kv_heads: int, dim: int, vdim: int, conv: int = 4, ff: int = 0) -> dict:
+    return dict(type="delta", mixer=dict(conv=conv, dim=dim, heads=heads, kv_heads=kv_heads, vdim=vdim), mlp=dict(ff=ff, kind="dense") if ff else None)
+
+
+def gobesun_attention_layer(heads: int, kv_heads: int, dim: int, vdim: int, chunk: int, rot_dims: int, ff: int = 0, base: float = 10000.0,
+                            scaling: dict = None, scale: float = None) -> dict:
+    rot = dict(base=base, dims=rot_dims)
+    if scaling:
+        rot["scaling"] = scaling
+    return dict(type="attention", mixer=dict(dim=dim, heads=heads, kv_heads=kv_heads, vdim=vdim, mask=dict(size=chunk), rot=rot,
+                                             scale=dim ** -0.5 if scale is None else scale), mlp=dict(ff=ff, kind="dense") if ff else None)
+
+
+def gobesun_config(width: int, vocab: int, layers: list, loop: dict = None, eps: float = 1e-6, embedding_scale: float = None) -> dict:
+    return dict(architecture="Gobesun", embedding=dict(scale=width ** 0.5 if embedding_scale is None else embedding_scale), layers=layers,
+                loop=loop or dict(start=0, stop=0, times=1), norm=dict(eps=eps), vocab=vocab, width=width)
+
+
+def gobesun_weights(cfg: dict, seed: int = 0, device="cpu") -> dict:
+    """name -> bf16 tensor, with the magnitudes of a model at initialisation (unit-variance activations through every sublayer)."""
+    g = torch.Generator().manual_seed(seed)
+    D = cfg["width"]
+    out = {}
+    rnd = lambda *shape, std=1.0: (torch.randn(*shape, generator=g) * std)
+    lin = lambda n, k: rnd(n, k, std=k ** -0.5)
+    out["embed"] = rnd(cfg["vocab"], D, std=D ** -0.5)
+    out["head"] = lin(cfg["vocab"], D)
+    out["final.norm"] = rnd(D, std=0.2)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        out[p + "norm1"], out[p + "norm1b"] = rnd(D, std=0.2), rnd(D, std=0.2)
+        if L["type"] == "delta":
+            out[p + "mix.q"], out[p + "mix.k"], out[p + "mix.v"], out[p + "mix.g"] = lin(G * dk, D), lin(G * dk, D), lin(H * dv, D), lin(H * dv, D)
+            for n, c in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
+                out[p + f"mix.{n}.conv"] = rnd(c, m["conv"], std=0.6) + 0.2
+            out[p + "mix.b"], out[p + "mix.a"] = lin(H, D), lin(H, D)
+            out[p + "mix.A_log"] = torch.rand(H, generator=g) * 4.0 - 4.0
+            out[p + "mix.dt_bias"] = torch.rand(H, generator=g) * 3.0 - 4.0
+            out[p + "mix.norm"] = 1.0 + rnd(dv, std=0.2)
+            out[p + "mix.o"] = lin(D, H * dv)
+        else:
+            out[p + "mix.q"], out[p + "mix.k"], out[p + "mix.v"] = lin(H * dk, D), lin(G * dk, D), lin(G * dv, D)
+            out[p + "mix.q.norm"], out[p + "mix.k.norm"] = 1.2 + rnd(H * dk, std=0.4), 1.2 + rnd(G * dk, std=0.4)
+            out[p + "mix.o"] = lin(D, H * dv)
+        if L.get("mlp"):
+            ff = L["mlp"]["ff"]
+            out[p + "norm2"], out[p + "norm2b"] = rnd(D, std=0.2), rnd(D, std=0.2)
+            out[p + "mlp.gate"], out[p + "mlp.up"], out[p + "mlp.down"] = lin(ff, D), lin(ff, D), lin(D, ff)
+    return {k: v.to(torch.bfloat16).to(device) for k, v in out.items()}

@@ -115,11 +115,26 @@ def rotate(x: torch.Tensor, cos, sin, dims: int) -> torch.Tensor:
 
 
 def visible(i: int, j: int, mask: Optional[dict]) -> bool:
+    """may the query at position i look at the key at position j?"""
     if j > i:
         return False
     if mask and "size" in mask:
         return i // mask["size"] == j // mask["size"]
     return True
+
+
+def masked_attention(q, k, v, scale: float, mask: Optional[dict], pos) -> torch.Tensor:
+    """q [T, H, dk], k [T, G, dk], v [T, G, dv] of one sequence whose rows sit at positions pos [T] -> [T, H, dv]."""
+    T, H, _ = q.shape
+    G, dv = k.shape[1], v.shape[-1]
+    rep = H // G
+    allowed = torch.tensor([[visible(int(pos[a]), int(pos[b]), mask) for b in range(T)] for a in range(T)])
+    out = torch.zeros(T, H, dv, dtype=F)
+    for hd in range(H):
+        s = (q[:, hd] @ k[:, hd // rep].T) * scale
+        s = s.masked_fill(~allowed, float("-inf"))
+        out[:, hd] = torch.softmax(s, dim=-1) @ v[:, hd // rep]
+    return out
 
 
 def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], m: dict, eps: float, positions=None) -> torch.Tensor:
@@ -134,13 +149,7 @@ def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], m: dict, eps: f
     if rot:
         cos, sin = rotary_angles(rot, pos)
         q, k = rotate(q, cos, sin, rot["dims"]), rotate(k, cos, sin, rot["dims"])
-    rep = H // G
-    out = torch.zeros(T, H, dv, dtype=F)
-    allowed = torch.tensor([[visible(int(pos[a]), int(pos[b]), m.get("mask")) for b in range(T)] for a in range(T)])
-    for hd in range(H):
-        s = (q[:, hd] @ k[:, hd // rep].T) * m["scale"]
-        s = s.masked_fill(~allowed, float("-inf"))
-        out[:, hd] = torch.softmax(s, dim=-1) @ v[:, hd // rep]
+    out = masked_attention(q, k, v, m["scale"], m.get("mask"), pos)
     return out.reshape(T, H * dv) @ W["o"].T
 
 
