@@ -29,10 +29,11 @@ def _generate(argv) -> int:
     ap.add_argument("--num-blocks", type=int, default=256)
     ap.add_argument("--max-num-seqs", type=int, default=4)
     ap.add_argument("--prefill-chunk", type=int, default=512)
+    ap.add_argument("--decode-graphs", action="store_true", help="replay captured CUDA graphs for steps of single tokens")
     a = ap.parse_args(argv)
     prompts = [[int(t) for t in p.split(",") if t.strip()] for p in a.prompt_ids]
     eng = LLMEngine.from_pretrained(a.model, dtype=torch.bfloat16 if a.dtype == "bfloat16" else torch.float32, num_blocks=a.num_blocks,
-                                    max_num_seqs=a.max_num_seqs, prefill_chunk=a.prefill_chunk,
+                                    max_num_seqs=a.max_num_seqs, prefill_chunk=a.prefill_chunk, decode_graphs=a.decode_graphs,
                                     max_model_len=max(len(p) for p in prompts) + a.max_new_tokens + 1)
     sp = SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p, max_tokens=a.max_new_tokens, seed=a.seed)
     for p, out in zip(prompts, eng.generate(prompts, sp)):

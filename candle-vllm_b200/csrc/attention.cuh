@@ -38,6 +38,6 @@ bool paged_attention_prefill_tc_supported(int head_dim, int block_size, int dtyp
                                           const void* q, const void* kc, const void* vc);
 void paged_attention_prefill_tc(void* out, const void* q, const void* kc, const void* vc, const uint32_t* block_tables, const uint32_t* cu_q,
                                 const uint32_t* cu_k, int num_seqs, int total_q, int num_heads, int num_kv_heads, int max_blocks, int64_t num_blocks,
-                                float scale, int window, int dtype, cudaStream_t st);
+                                float scale, int window, int dtype, cudaStream_t st, int chunk = 0);
 
 }  // namespace b200

@@ -76,6 +76,7 @@ struct PrefillParams {
     const void* q; void* out;
     const uint32_t* block_tables; const uint32_t* cu_q; const uint32_t* cu_k;
     int num_seqs, num_heads, num_kv_heads, max_blocks, window;
+    int chunk;                      // > 0: a query at position i sees key j only if j / chunk == i / chunk
     float scale_log2;
 };
 
@@ -105,7 +106,8 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     const int rows = min(kQTile, qlen - q0);
     const int pos0 = klen - qlen + q0;                              // context position of tile row 0 (bottom-right aligned causal mask)
     const int last_pos = pos0 + rows - 1;
-    const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    if (p.chunk > 0) first_key = max(first_key, (pos0 / p.chunk) * p.chunk);       // row 0 has the earliest chunk start of the tile
     const int page_lo = first_key / kPg, page_hi = last_pos / kPg;  // pages [page_lo, page_hi] hold every visible key
     const uint32_t* table = p.block_tables + (int64_t)seq * p.max_blocks;
 
@@ -150,6 +152,8 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
     const int pos_lo = pos0 + r_lo, pos_hi = pos0 + r_hi;          // last visible key of each of this thread's two rows
     const int warp_min_pos = pos0 + warp * 16, warp_max_pos = pos0 + warp * 16 + 15;
+    const int cs_lo = p.chunk > 0 ? (pos_lo / p.chunk) * p.chunk : 0, cs_hi = p.chunk > 0 ? (pos_hi / p.chunk) * p.chunk : 0;
+    const int warp_min_cs = p.chunk > 0 ? (warp_min_pos / p.chunk) * p.chunk : 0, warp_max_cs = p.chunk > 0 ? (warp_max_pos / p.chunk) * p.chunk : 0;
 
     for (int page = page_lo, it = 0; page <= page_hi; ++page, ++it) {
         const int stage = it & 1;
@@ -160,6 +164,7 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             const int tok0 = page * kPg + h * kHalf;                 // first token of this 32-token half
             if (tok0 > warp_max_pos) break;                          // entirely in the future of every row of this warp
             if (p.window > 0 && tok0 + kHalf - 1 < warp_min_pos - p.window + 1) continue;      // entirely before every row's window
+            if (tok0 + kHalf - 1 < warp_min_cs) continue;                                      // entirely before every row's chunk
             const uint32_t kt = smem_base + stage * kStage + h * 4 * kSub, vt = kt + 2 * kSub;
             // ---- S = Q K^T : 4 n-tiles (8 tokens) x 8 k-steps -----------------------------------------------------------------
             float sacc[4][4];
@@ -178,7 +183,7 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
                 }
             }
             // ---- mask (only where the half touches the diagonal / window edge / context end) + online softmax --------------------
-            const bool need_mask = tok0 + kHalf - 1 > warp_min_pos || (p.window > 0 && tok0 < warp_max_pos - p.window + 1);
+            const bool need_mask = tok0 + kHalf - 1 > warp_min_pos || (p.window > 0 && tok0 < warp_max_pos - p.window + 1) || tok0 < warp_max_cs;
             float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt) {
@@ -187,8 +192,8 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
                     const int tok = tok0 + nt * 8 + 2 * t + e;
                     bool ok_lo = true, ok_hi = true;
                     if (need_mask) {
-                        ok_lo = tok <= pos_lo && (p.window <= 0 || tok > pos_lo - p.window);
-                        ok_hi = tok <= pos_hi && (p.window <= 0 || tok > pos_hi - p.window);
+                        ok_lo = tok <= pos_lo && (p.window <= 0 || tok > pos_lo - p.window) && tok >= cs_lo;
+                        ok_hi = tok <= pos_hi && (p.window <= 0 || tok > pos_hi - p.window) && tok >= cs_hi;
                     }
                     sacc[nt][e] = ok_lo ? sacc[nt][e] * p.scale_log2 : -INFINITY;
                     sacc[nt][2 + e] = ok_hi ? sacc[nt][2 + e] * p.scale_log2 : -INFINITY;
@@ -292,13 +297,13 @@ bool paged_attention_prefill_tc_supported(int head_dim, int block_size, int dtyp
 // DEVICE-side cu_seqlens, so a graph captured with padded metadata replays correctly)
 void paged_attention_prefill_tc(void* out, const void* q, const void* kc, const void* vc, const uint32_t* block_tables, const uint32_t* cu_q,
                                 const uint32_t* cu_k, int num_seqs, int total_q, int num_heads, int num_kv_heads, int max_blocks, int64_t num_blocks,
-                                float scale, int window, int dtype, cudaStream_t st) {
+                                float scale, int window, int dtype, cudaStream_t st, int chunk) {
     CUtensorMap km, vm;
     if (!make_kv_map(&km, kc, num_blocks, num_kv_heads, dtype) || !make_kv_map(&vm, vc, num_blocks, num_kv_heads, dtype)) {
         set_error(kErrCuda, "paged_attention_prefill: cuTensorMapEncodeTiled failed");
         return;
     }
-    PrefillParams p{q, out, block_tables, cu_q, cu_k, num_seqs, num_heads, num_kv_heads, max_blocks, window, scale * 1.4426950408889634f};
+    PrefillParams p{q, out, block_tables, cu_q, cu_k, num_seqs, num_heads, num_kv_heads, max_blocks, window, chunk, scale * 1.4426950408889634f};
     const int tiles = total_q / kQTile + num_seqs;                   // >= sum of ceil(q_len / 64)
     if (dtype == B200_BF16) {
         ensure_dynamic_smem(reinterpret_cast<const void*>(paged_attn_prefill_kernel<__nv_bfloat16>), kPfSmem);

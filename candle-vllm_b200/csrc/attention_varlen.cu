@@ -11,16 +11,19 @@
 //                           written into the paged cache at slot_mapping[t] (K [nb, bs, G, dk], V [nb, bs, G, dv]).
 //   paged_attention_varlen  one warp per (token, head); keys in tiles of 32 (a lane scores one key, the tile's values are then
 //                           accumulated with lanes across the value columns), online softmax in f32.
+#include <stdlib.h>
+
+#include "attention.cuh"
 #include "common.cuh"
 
 namespace b200 {
 namespace {
 
-template <typename TC>
+template <typename TC, typename TQ>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int32_t* __restrict__ positions,
-                          const int64_t* __restrict__ slot_mapping, float* __restrict__ q_out, TC* __restrict__ k_cache,
+                          const int64_t* __restrict__ slot_mapping, TQ* __restrict__ q_out, TC* __restrict__ k_cache,
                           TC* __restrict__ v_cache, int H, int G, int dk, int dv, int rot_dims, float eps) {
     __shared__ float red[2][8];
     const int t = blockIdx.x;
@@ -57,7 +60,7 @@ qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float
             const float s = sin_t[(int64_t)pos * half + (d < half ? d : d - half)];
             val = d < half ? val * c - other * s : val * c + other * s;
         }
-        if (is_q) q_out[(int64_t)t * nq + idx] = val;
+        if (is_q) q_out[(int64_t)t * nq + idx] = from_f32<TQ>(val);
         else if (slot >= 0) k_cache[slot * nk + idx] = from_f32<TC>(val);
     }
     if (slot >= 0)
@@ -66,9 +69,9 @@ qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float
 
 constexpr int kMaxVPerLane = 8;      // value size <= 256
 
-template <typename TC, typename TOut>
+template <typename TC, typename TOut, typename TQ>
 __global__ void __launch_bounds__(128)
-paged_attention_varlen_kernel(const float* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
+paged_attention_varlen_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                               const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ token_seq,
                               const int32_t* __restrict__ positions, TOut* __restrict__ out, int64_t items, int H, int G, int dk, int dv,
                               int block_size, float scale, int chunk, int window) {
@@ -82,7 +85,7 @@ paged_attention_varlen_kernel(const float* __restrict__ q, const TC* __restrict_
     const int pos = positions[t];
     const int32_t* table = block_tables + (int64_t)token_seq[t] * table_width;
     float* qs = qsm + warp * dk;
-    for (int i = lane; i < dk; i += 32) qs[i] = q[((int64_t)t * H + h) * dk + i] * scale;
+    for (int i = lane; i < dk; i += 32) qs[i] = to_f32<TQ>(q[((int64_t)t * H + h) * dk + i]) * scale;
     __syncwarp();
     int lo = 0;
     if (chunk > 0) lo = (pos / chunk) * chunk;
@@ -138,9 +141,9 @@ using namespace b200;
 extern "C" {
 
 void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, const float* k_norm_w, const float* cos_t, const float* sin_t,
-                        int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, float* q_out, void* key_cache, void* value_cache,
+                        int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, void* q_out, void* key_cache, void* value_cache,
                         int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,
-                        int32_t cache_dtype, int64_t stream) {
+                        int32_t cache_dtype, int32_t q_dtype, int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(qkv && positions && slot_mapping && q_out && key_cache && value_cache, kErrBadArg, "qk_norm_rope_cache: null pointer");
     B200_REQUIRE((q_norm_w == nullptr) == (k_norm_w == nullptr) && (cos_t == nullptr) == (sin_t == nullptr), kErrBadArg,
@@ -149,38 +152,49 @@ void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, con
                  ld >= (int64_t)num_heads * dk + (int64_t)num_kv_heads * (dk + dv) && (!cos_t || max_pos > 0),
                  kErrBadArg, "qk_norm_rope_cache: bad sizes");
     cudaStream_t st = as_stream(stream);
-    if (cache_dtype == B200_F32)
-        qk_norm_rope_cache_kernel<float><<<num_tokens, 256, 0, st>>>(qkv, ld, q_norm_w, k_norm_w, cos_t, sin_t, positions, slot_mapping, q_out,
-                                                                     (float*)key_cache, (float*)value_cache, num_heads, num_kv_heads, dk, dv, rot_dims, eps);
-    else if (cache_dtype == B200_BF16)
-        qk_norm_rope_cache_kernel<__nv_bfloat16><<<num_tokens, 256, 0, st>>>(qkv, ld, q_norm_w, k_norm_w, cos_t, sin_t, positions, slot_mapping, q_out,
-                                                                             (__nv_bfloat16*)key_cache, (__nv_bfloat16*)value_cache, num_heads,
-                                                                             num_kv_heads, dk, dv, rot_dims, eps);
-    else { set_error(kErrUnsupported, "qk_norm_rope_cache: cache dtype %d (f32 / bf16)", cache_dtype); return; }
+#define QNRC(TC, TQ) qk_norm_rope_cache_kernel<TC, TQ><<<num_tokens, 256, 0, st>>>(qkv, ld, q_norm_w, k_norm_w, cos_t, sin_t, positions, slot_mapping, \
+        (TQ*)q_out, (TC*)key_cache, (TC*)value_cache, num_heads, num_kv_heads, dk, dv, rot_dims, eps)
+    if (cache_dtype == B200_F32 && q_dtype == B200_F32) QNRC(float, float);
+    else if (cache_dtype == B200_BF16 && q_dtype == B200_F32) QNRC(__nv_bfloat16, float);
+    else if (cache_dtype == B200_BF16 && q_dtype == B200_BF16) QNRC(__nv_bfloat16, __nv_bfloat16);
+    else { set_error(kErrUnsupported, "qk_norm_rope_cache: cache dtype %d / q dtype %d", cache_dtype, q_dtype); return; }
+#undef QNRC
     count_launch();
     check_launch("qk_norm_rope_cache");
 }
 
-void paged_attention_varlen(void* out, const float* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,
-                            int32_t table_width, const int32_t* token_seq, const int32_t* positions, int32_t num_tokens, int32_t num_heads,
-                            int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t block_size, float scale, int32_t chunk, int32_t window,
-                            int32_t cache_dtype, int32_t out_dtype, int64_t stream) {
+void paged_attention_varlen(void* out, const void* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,
+                            int32_t table_width, const int32_t* token_seq, const int32_t* positions, const int32_t* cu_seqlens_q,
+                            const int32_t* cu_seqlens_k, int32_t num_seqs, int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk,
+                            int32_t dv, int32_t block_size, float scale, int32_t chunk, int32_t window, int32_t q_dtype, int32_t cache_dtype,
+                            int32_t out_dtype, int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(out && q && key_cache && value_cache && block_tables && token_seq && positions, kErrBadArg, "paged_attention_varlen: null pointer");
     B200_REQUIRE(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dk > 0 && dv > 0 && block_size > 0 && table_width > 0,
                  kErrBadArg, "paged_attention_varlen: bad sizes");
+    cudaStream_t st = as_stream(stream);
+    // 16-bit q / cache / out with 128-wide heads and 64-token blocks: the tensor-core kernel that serves the other models' prefill
+    // (attention_prefill.cu), with the chunk rule added to its mask; it covers portions and single tokens alike
+    static const bool no_tc = [] { const char* e = getenv("B200_VARLEN_SIMT"); return e && atoi(e) != 0; }();
+    if (!no_tc && q_dtype == B200_BF16 && out_dtype == B200_BF16 && dk == dv && cu_seqlens_q && cu_seqlens_k && num_seqs > 0 &&
+        paged_attention_prefill_tc_supported(dk, block_size, B200_BF16, cache_dtype, B200_KV_FLASH, 0.f, 1, q, key_cache, value_cache)) {
+        paged_attention_prefill_tc(out, q, key_cache, value_cache, (const uint32_t*)block_tables, (const uint32_t*)cu_seqlens_q,
+                                   (const uint32_t*)cu_seqlens_k, num_seqs, num_tokens, num_heads, num_kv_heads, table_width, (int64_t)1 << 22, scale,
+                                   window, B200_BF16, st, chunk);
+        return;
+    }
     B200_REQUIRE(dv <= 32 * kMaxVPerLane && dk <= 2048, kErrUnsupported, "paged_attention_varlen: value size %d > %d or key size %d > 2048", dv,
                  32 * kMaxVPerLane, dk);
     const int64_t items = (int64_t)num_tokens * num_heads;
     const unsigned grid = (unsigned)((items + 3) / 4);
     const size_t smem = (size_t)4 * dk * sizeof(float);
-    cudaStream_t st = as_stream(stream);
-#define PAV(TC, TO) paged_attention_varlen_kernel<TC, TO><<<grid, 128, smem, st>>>(q, (const TC*)key_cache, (const TC*)value_cache, block_tables, \
+#define PAV(TC, TO, TQ) paged_attention_varlen_kernel<TC, TO, TQ><<<grid, 128, smem, st>>>((const TQ*)q, (const TC*)key_cache, (const TC*)value_cache, block_tables, \
         table_width, token_seq, positions, (TO*)out, items, num_heads, num_kv_heads, dk, dv, block_size, scale, chunk, window)
-    if (cache_dtype == B200_F32 && out_dtype == B200_F32) PAV(float, float);
-    else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16) PAV(__nv_bfloat16, __nv_bfloat16);
-    else if (cache_dtype == B200_BF16 && out_dtype == B200_F32) PAV(__nv_bfloat16, float);
-    else { set_error(kErrUnsupported, "paged_attention_varlen: cache dtype %d / out dtype %d", cache_dtype, out_dtype); return; }
+    if (cache_dtype == B200_F32 && out_dtype == B200_F32 && q_dtype == B200_F32) PAV(float, float, float);
+    else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16 && q_dtype == B200_F32) PAV(__nv_bfloat16, __nv_bfloat16, float);
+    else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16 && q_dtype == B200_BF16) PAV(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else if (cache_dtype == B200_BF16 && out_dtype == B200_F32 && q_dtype == B200_F32) PAV(__nv_bfloat16, float, float);
+    else { set_error(kErrUnsupported, "paged_attention_varlen: cache dtype %d / out dtype %d / q dtype %d", cache_dtype, out_dtype, q_dtype); return; }
 #undef PAV
     count_launch();
     check_launch("paged_attention_varlen");

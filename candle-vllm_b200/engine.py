@@ -24,8 +24,55 @@ from .seq_ops import StepBatch
 from .state_cache import StateCache
 
 
+class _DecodeGraph:
+    """A captured step of B single-token entries (the reference replays captured decode graphs the same way,
+    /root/reference/src/backend/graph.rs:685-803): static metadata buffers, two small H2D copies and one graph launch per step.
+    Warm-up runs on a scratch state slot with the cache write switched off, so capturing disturbs no live sequence."""
+
+    def __init__(self, runner: "ModelRunner", B: int, width: int):
+        dev = runner.model.device
+        self.B, self.W = B, width
+        n = B * (4 + width) + B + 1
+        self.host = torch.zeros(n, dtype=torch.int32).pin_memory()
+        self.host_slots = torch.zeros(B, dtype=torch.int64).pin_memory()
+        self.meta = torch.zeros(n, dtype=torch.int32, device=dev)
+        m = self.meta
+        ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        self.batch = StepBatch(tokens=m[0:B], positions=m[B:2 * B], token_seq=ar[:B].clone(), slot_mapping=torch.full((B,), -1, dtype=torch.int64, device=dev),
+                               cu_seqlens=ar, cu_seqlens_k=m[4 * B + B * width:], seq_slots=m[2 * B:3 * B], seq_start=m[3 * B:4 * B],
+                               block_tables=m[4 * B:4 * B + B * width].view(B, width),
+                               want_rows=ar[:B].clone(), num_tokens=B, num_seqs=B, num_want=B, max_position=0)
+        self.meta[2 * B:3 * B] = runner.state.scratch_slot
+        self.meta[4 * B + B * width:] = ar                     # warm-up: one key per entry
+        kv = runner.cache.gpu_cache if runner.cache else []
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                runner.model.forward(self.batch, kv, runner.state.tensors)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = runner.model.forward(self.batch, kv, runner.state.tensors)
+
+    def replay(self, prep: dict) -> torch.Tensor:
+        B, h = self.B, self.host.numpy()
+        h[0:B], h[B:2 * B], h[2 * B:3 * B], h[3 * B:4 * B] = prep["tokens"], prep["positions"], prep["seq_slots"], prep["seq_start"]
+        bt = prep["block_tables"]
+        tab = h[4 * B:4 * B + B * self.W].reshape(B, self.W)
+        tab[:, :bt.shape[1]] = bt
+        h[4 * B + B * self.W:] = prep["cu_seqlens_k"]
+        self.host_slots.numpy()[:] = prep["slot_mapping"]
+        self.meta.copy_(self.host, non_blocking=True)
+        self.batch.slot_mapping.copy_(self.host_slots, non_blocking=True)
+        self.graph.replay()
+        return self.logits
+
+
 class ModelRunner:
-    def __init__(self, model, num_blocks: int, num_slots: int, block_size: int = 64):
+    def __init__(self, model, num_blocks: int, num_slots: int, block_size: int = 64, decode_graphs: bool = False, max_blocks_per_seq: int = 0):
+        """``decode_graphs``: steps made of single tokens only (one wanted logit each) replay a CUDA graph captured per batch size;
+        ``max_blocks_per_seq`` is the table width those graphs are captured with (default: the whole pool)."""
         self.model, self.block_size = model, block_size
         plan = model.cache_plan()
         kv = plan["kv_layers"]
@@ -33,6 +80,9 @@ class ModelRunner:
         self.state = StateCache(plan["state_layers"], num_slots, device=model.device)
         self.blocks = BlockManager(block_size, num_blocks, 0)
         self.lengths: Dict[int, int] = {}          # tokens of each live sequence already in cache / state
+        self.decode_graphs = decode_graphs
+        self.graph_width = max_blocks_per_seq or num_blocks
+        self._graphs: Dict[int, _DecodeGraph] = {}
 
     # -- sequence lifetime -------------------------------------------------------------------------------------------
     def can_admit(self, num_tokens: int, reserved_blocks: int = 0) -> bool:
@@ -63,8 +113,18 @@ class ModelRunner:
             start = self.lengths[sid]
             table = self.blocks.grow_to(sid, start + len(toks))
             rows.append(dict(tokens=toks, start=start, block_table=table, state_slot=self.state.pool.slot_of(sid), want=e.get("want", ())))
-        batch = StepBatch.from_host(prepare_step(rows, self.block_size), self.model.device)
-        logits = self.model.forward(batch, self.cache.gpu_cache if self.cache else [], self.state.tensors, hidden_trace)
+        prep = prepare_step(rows, self.block_size)
+        if (self.decode_graphs and hidden_trace is None and all(len(e["tokens"]) == 1 and list(e.get("want", ())) == [0] for e in entries)
+                and prep["block_tables"].shape[1] <= self.graph_width):
+            if self.model.ensure_positions(int(prep["max_position"]) + 1):
+                self._graphs.clear()             # captured steps point at the old tables
+            g = self._graphs.get(len(entries))
+            if g is None:
+                g = self._graphs[len(entries)] = _DecodeGraph(self, len(entries), self.graph_width)
+            logits = g.replay(prep)
+        else:
+            batch = StepBatch.from_host(prep, self.model.device)
+            logits = self.model.forward(batch, self.cache.gpu_cache if self.cache else [], self.state.tensors, hidden_trace)
         for e in entries:
             self.lengths[e["seq_id"]] += len(e["tokens"])
         return logits
@@ -136,9 +196,9 @@ class Scheduler:
 
 class LLMEngine:
     def __init__(self, model, num_blocks: int = 256, max_num_seqs: int = 4, block_size: int = 64, max_batch_tokens: int = 2048,
-                 prefill_chunk: int = 512):
+                 prefill_chunk: int = 512, decode_graphs: bool = False, max_blocks_per_seq: int = 0):
         self.model = model
-        self.runner = ModelRunner(model, num_blocks, max_num_seqs, block_size)
+        self.runner = ModelRunner(model, num_blocks, max_num_seqs, block_size, decode_graphs=decode_graphs, max_blocks_per_seq=max_blocks_per_seq)
         self.scheduler = Scheduler(self.runner, max_batch_tokens, max_num_seqs, prefill_chunk)
         self.sampler = Sampler()
         self._next_id = 0

@@ -117,6 +117,15 @@ class GobesunModel:
         cfg = GobesunConfig.from_json(os.path.join(path, "config.json"))
         return cls(cfg, load_file(os.path.join(path, "model.safetensors")), dtype=dtype, **kw)
 
+    def ensure_positions(self, max_pos: int) -> bool:
+        """grow the rotary tables (outside any graph capture) to cover positions below ``max_pos``; True if a table moved"""
+        moved = False
+        for L in self.layers:
+            if L.mixer.kind == "kv" and L.mixer.rot and L.mixer.cos.shape[0] < max_pos:
+                L.mixer.ensure_positions(max(2 * L.mixer.cos.shape[0], max_pos))
+                moved = True
+        return moved
+
     def cache_plan(self) -> dict:
         """What the engine allocates: one (kv heads, key size, value size) per attention run, one tuple of per-slot state shapes per
         recurrent run, in run order."""

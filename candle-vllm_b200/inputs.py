@@ -102,9 +102,10 @@ def prepare_step(entries: Sequence[dict], block_size: int) -> dict:
     steps, inputs.rs:90-374 / :376-454; the layout below is the union of both).  Each entry is a dict with ``tokens`` (the ids this step
     brings for the sequence), ``start`` (position of the first of them), ``block_table`` (covering start + len(tokens) positions),
     ``state_slot`` (recurrent-state slot, -1 if the model has none) and ``want`` (indices into ``tokens`` whose logits are asked for).
-    Rows are laid out entry after entry."""
+    Rows are laid out entry after entry; ``cu_seqlens`` counts rows, ``cu_seqlens_k`` the keys each entry's last row sees without a mask
+    (start + len(tokens)), the pair the prefill attention kernel takes."""
     tokens, positions, token_seq, slots, want_rows = [], [], [], [], []
-    cu, seq_slots, seq_start, tabs = [0], [], [], []
+    cu, cu_k, seq_slots, seq_start, tabs = [0], [0], [], [], []
     for b, e in enumerate(entries):
         toks, start, table = e["tokens"], int(e["start"]), e["block_table"]
         if len(toks) == 0:
@@ -118,11 +119,11 @@ def prepare_step(entries: Sequence[dict], block_size: int) -> dict:
             if not 0 <= int(w) < len(toks):
                 raise BackendError(f"prepare_step: wanted index {w} outside the entry's {len(toks)} tokens")
             want_rows.append(base + int(w))
-        cu.append(base + len(toks))
+        cu.append(base + len(toks)); cu_k.append(cu_k[-1] + start + len(toks))
         seq_slots.append(int(e.get("state_slot", -1))); seq_start.append(start)
         tabs.append(list(table[:used_blocks_for_len(start + len(toks), block_size, len(table))]))
     return dict(tokens=np.asarray(tokens, np.int32), positions=np.asarray(positions, np.int32), token_seq=np.asarray(token_seq, np.int32),
-                slot_mapping=np.asarray(slots, np.int64), cu_seqlens=np.asarray(cu, np.int32), seq_slots=np.asarray(seq_slots, np.int32),
+                slot_mapping=np.asarray(slots, np.int64), cu_seqlens=np.asarray(cu, np.int32), cu_seqlens_k=np.asarray(cu_k, np.int32), seq_slots=np.asarray(seq_slots, np.int32),
                 seq_start=np.asarray(seq_start, np.int32), block_tables=_pad_tables(tabs), want_rows=np.asarray(want_rows, np.int32),
                 max_position=max(positions) if positions else 0)
 

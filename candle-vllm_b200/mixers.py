@@ -93,6 +93,8 @@ class PagedAttentionMixer:
         self.rot_dims = int(rot["dims"]) if rot else 0
         if self.rot_dims % 2 or self.rot_dims > dk:
             raise BackendError(f"PagedAttentionMixer: {self.rot_dims} rotary dims do not fit a head of {dk}")
+        # 16-bit q for the tensor-core attention kernel (128-wide heads, 64-token blocks, bf16 cache); f32 q for the SIMT one
+        self.q_dtype = torch.bfloat16 if (dtype == torch.bfloat16 and dk == dv == 128 and block_size == 64) else torch.float32
         self.cos = self.sin = None
         self._device = self.w_in.device
         if rot:
@@ -111,7 +113,7 @@ class PagedAttentionMixer:
             self.ensure_positions(max(2 * self.cos.shape[0], batch.max_position + 1))
         proj = ops.linear(h, self.w_in)
         q = ops.qk_norm_rope_cache(proj, self.q_norm, self.k_norm, self.cos, self.sin, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dv,
-                                   self.rot_dims, self.eps)
+                                   self.rot_dims, self.eps, self.q_dtype)
         a = ops.paged_attention_varlen(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.dv, self.block_size, self.scale, self.chunk,
                                        self.window, self.dtype)
         return ops.linear(a, self.w_o)

@@ -34,7 +34,8 @@ class StepBatch:
     positions: torch.Tensor       # [T] position of each row in its sequence
     token_seq: torch.Tensor       # [T] entry that owns the row
     slot_mapping: torch.Tensor    # [T] i64, flat cache slot = block * block_size + offset
-    cu_seqlens: torch.Tensor      # [B + 1]
+    cu_seqlens: torch.Tensor      # [B + 1] rows
+    cu_seqlens_k: torch.Tensor    # [B + 1] context lengths (start + rows), cumulative
     seq_slots: torch.Tensor       # [B] state slot of each entry's sequence
     seq_start: torch.Tensor       # [B] position of each entry's first row (0 = new sequence)
     block_tables: torch.Tensor    # [B, W]
@@ -48,7 +49,7 @@ class StepBatch:
     def from_host(cls, prep: dict, device="cuda") -> "StepBatch":
         t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dt)).to(device, non_blocking=True)
         return cls(tokens=t(prep["tokens"], np.int32), positions=t(prep["positions"], np.int32), token_seq=t(prep["token_seq"], np.int32),
-                   slot_mapping=t(prep["slot_mapping"], np.int64), cu_seqlens=t(prep["cu_seqlens"], np.int32),
+                   slot_mapping=t(prep["slot_mapping"], np.int64), cu_seqlens=t(prep["cu_seqlens"], np.int32), cu_seqlens_k=t(prep["cu_seqlens_k"], np.int32),
                    seq_slots=t(prep["seq_slots"], np.int32), seq_start=t(prep["seq_start"], np.int32),
                    block_tables=t(prep["block_tables"], np.int32), want_rows=t(prep["want_rows"], np.int32),
                    num_tokens=len(prep["tokens"]), num_seqs=len(prep["seq_slots"]), num_want=len(prep["want_rows"]),
@@ -141,15 +142,15 @@ def gated_rms_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, he
 
 def qk_norm_rope_cache(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], cos: Optional[torch.Tensor],
                        sin: Optional[torch.Tensor], batch: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int, kv_heads: int, dk: int,
-                       dv: int, rot_dims: int, eps: float) -> torch.Tensor:
+                       dv: int, rot_dims: int, eps: float, q_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     T = qkv.shape[0]
     if cos is not None and batch.max_position >= cos.shape[0]:
         raise BackendError(f"position {batch.max_position} is outside the rotary table ({cos.shape[0]} rows)")
-    q = torch.empty((T, heads * dk), dtype=torch.float32, device=qkv.device)
+    q = torch.empty((T, heads * dk), dtype=q_dtype, device=qkv.device)
     lib().qk_norm_rope_cache(_ptr(qkv), C.c_int64(qkv.stride(0) if T > 1 else qkv.shape[1]), _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin),
                              C.c_int32(0 if cos is None else cos.shape[0]), _ptr(batch.positions), _ptr(batch.slot_mapping), _ptr(q), _ptr(k_cache),
                              _ptr(v_cache), C.c_int32(T), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk), C.c_int32(dv), C.c_int32(rot_dims),
-                             C.c_float(eps), C.c_int32(_tag(k_cache.dtype)), _stream(qkv.device))
+                             C.c_float(eps), C.c_int32(_tag(k_cache.dtype)), C.c_int32(_tag(q_dtype)), _stream(qkv.device))
     check("qk_norm_rope_cache")
     return q
 
@@ -159,8 +160,9 @@ def paged_attention_varlen(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     T = q.shape[0]
     out = torch.empty((T, heads * dv), dtype=out_dtype, device=q.device)
     lib().paged_attention_varlen(_ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables), C.c_int32(batch.block_tables.shape[1]),
-                                 _ptr(batch.token_seq), _ptr(batch.positions), C.c_int32(T), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk),
-                                 C.c_int32(dv), C.c_int32(block_size), C.c_float(scale), C.c_int32(chunk), C.c_int32(window),
-                                 C.c_int32(_tag(k_cache.dtype)), C.c_int32(_tag(out_dtype)), _stream(q.device))
+                                 _ptr(batch.token_seq), _ptr(batch.positions), _ptr(batch.cu_seqlens), _ptr(batch.cu_seqlens_k), C.c_int32(batch.num_seqs),
+                                 C.c_int32(T), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk), C.c_int32(dv), C.c_int32(block_size), C.c_float(scale),
+                                 C.c_int32(chunk), C.c_int32(window), C.c_int32(_tag(q.dtype)), C.c_int32(_tag(k_cache.dtype)), C.c_int32(_tag(out_dtype)),
+                                 _stream(q.device))
     check("paged_attention_varlen")
     return out

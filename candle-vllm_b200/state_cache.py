@@ -53,8 +53,9 @@ class StateCache:
     def __init__(self, shapes: Sequence[Sequence[Tuple[int, ...]]], num_slots: int, device="cuda"):
         self.num_slots = int(num_slots)
         self.pool = SlotPool(num_slots)
+        self.scratch_slot = self.num_slots          # one slot past the pool: a place for warm-up steps to write
         self.tensors: List[Tuple[torch.Tensor, ...]] = [
-            tuple(torch.zeros((self.num_slots,) + tuple(s), dtype=torch.float32, device=device) for s in per_layer) for per_layer in shapes]
+            tuple(torch.zeros((self.num_slots + 1,) + tuple(s), dtype=torch.float32, device=device) for s in per_layer) for per_layer in shapes]
 
     def bytes_per_slot(self) -> int:
         return sum(t[0].numel() * 4 for per in self.tensors for t in per)

@@ -438,18 +438,20 @@ void gated_rms_norm(const float* o, const float* gate, int64_t ld_gate, const fl
 /* qk_norm_rope_cache: qkv f32 [T, H dk | G dk | G dv] (row pitch ld) -> optional RMS norm over the whole q row and the whole k row (weights
  *   f32 [H dk], [G dk]), optional rotation of the first rot_dims entries of each head (entry i with i + rot_dims/2) by cos / sin f32
  *   [max_pos, rot_dims/2], q_out f32 [T, H dk], K / V written at slot_mapping[t] (negative = skip) into caches [nb, bs, G, dk] / [nb, bs, G, dv]
- *   of cache_dtype F32 / BF16.
- * paged_attention_varlen: out[t, h, :] = softmax over the visible keys of (q[t, h] . k_j) * scale times v_j; key j of the token's sequence
+ *   of cache_dtype F32 / BF16; q_out of q_dtype F32 / BF16.
+ * paged_attention_varlen: q of q_dtype; with bf16 q / cache / out, dk == dv == 128 and 64-token blocks the step runs on the tensor-core kernel of
+ *   paged_attention_prefill (entry b's keys = cu_seqlens_k[b+1] - cu_seqlens_k[b], its rows the last of them), otherwise on a SIMT kernel. out[t, h, :] = softmax over the visible keys of (q[t, h] . k_j) * scale times v_j; key j of the token's sequence
  *   (block_tables i32 [num_seqs, table_width], row token_seq[t]) is visible to position i = positions[t] iff j <= i, j / chunk == i / chunk
  *   (chunk > 0) and i - j < window (window > 0).  dv <= 256.  out_dtype F32 / BF16. */
 void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, const float* k_norm_w, const float* cos_t, const float* sin_t,
-                        int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, float* q_out, void* key_cache, void* value_cache,
+                        int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, void* q_out, void* key_cache, void* value_cache,
                         int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,
-                        int32_t cache_dtype, int64_t stream);
-void paged_attention_varlen(void* out, const float* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,
-                            int32_t table_width, const int32_t* token_seq, const int32_t* positions, int32_t num_tokens, int32_t num_heads,
-                            int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t block_size, float scale, int32_t chunk, int32_t window,
-                            int32_t cache_dtype, int32_t out_dtype, int64_t stream);
+                        int32_t cache_dtype, int32_t q_dtype, int64_t stream);
+void paged_attention_varlen(void* out, const void* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,
+                            int32_t table_width, const int32_t* token_seq, const int32_t* positions, const int32_t* cu_seqlens_q,
+                            const int32_t* cu_seqlens_k, int32_t num_seqs, int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk,
+                            int32_t dv, int32_t block_size, float scale, int32_t chunk, int32_t window, int32_t q_dtype, int32_t cache_dtype,
+                            int32_t out_dtype, int64_t stream);
 
 /* library-wide count of kernels launched by this library (evidence for bench.py's gpu_launches) */
 long long b200_total_kernel_launches(void);

@@ -176,12 +176,13 @@ def test_attention_norm_rotation_cache_and_chunk_mask(H, Gk, dk, dv, chunk, rot_
         close(torch.cat(got), want, 5e-6, f"portions {sizes}")
 
 
-@pytest.mark.parametrize("chunk,bs", [(96, 64), (40, 16), (64, 64)])
-def test_attention_edges_show_a_key_one_off(chunk, bs):
+@pytest.mark.parametrize("chunk,bs,tc", [(96, 64, False), (40, 16, False), (64, 64, False), (96, 64, True), (40, 64, True), (64, 64, True), (130, 64, True)])
+def test_attention_edges_show_a_key_one_off(chunk, bs, tc):
     """One key per probe is made to dominate (its score stands far above the rest).  Queries at the first position of a chunk must not
     see the key just before them; queries at the last position of a chunk must see the chunk's first key; both across page borders."""
     H = Gk = 1
-    dk, dv, T = 8, 4, 3 * chunk + 5
+    dk, dv, T = (128, 128, 3 * chunk + 5) if tc else (8, 4, 3 * chunk + 5)      # tc: the shapes the tensor-core kernel takes (bf16 cache and q)
+    cdt, tol = (torch.bfloat16, 1e-2) if tc else (torch.float32, 1e-5)
     g = torch.Generator().manual_seed(chunk)
     q = torch.randn(T, 1, dk, generator=g) * 0.1
     k = torch.randn(T, 1, dk, generator=g) * 0.1
@@ -198,18 +199,56 @@ def test_attention_edges_show_a_key_one_off(chunk, bs):
             k[first, 0] = -40 * mark + k[first, 0] * 0; v[first, 0] = -50.0
             probes.append(first + chunk - 1)
     pos = torch.arange(T)
+    q, k, v = (x.to(cdt).float() for x in (q, k, v))
     want = G.masked_attention(q.to(F64), k.to(F64), v.to(F64), 1.0, dict(size=chunk), pos).reshape(T, dv)
     assert all(abs(float(want[p, 0])) < 60 for p in probes if p % chunk == 0)        # the loud outside key is not in the answer
     qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], 1)
     nb = -(-T // bs)
     for sizes in ([T], [1], [chunk - 1, 2, 1], [bs, 3]):
-        kc, vc = torch.zeros((nb, bs, 1, dk), device=DEV), torch.zeros((nb, bs, 1, dv), device=DEV)
+        kc, vc = torch.zeros((nb, bs, 1, dk), device=DEV, dtype=cdt), torch.zeros((nb, bs, 1, dv), device=DEV, dtype=cdt)
         got = []
         for at, n in _portions(T, sizes):
             b = batch_of([dict(tokens=[0] * n, start=at, block_table=list(range(nb)), state_slot=-1, want=[])], bs)
-            qq = ops.qk_norm_rope_cache(dev(qkv)[at:at + n], None, None, None, None, b, kc, vc, 1, 1, dk, dv, 0, 1e-6)
-            got.append(ops.paged_attention_varlen(qq, kc, vc, b, 1, 1, dk, dv, bs, 1.0, chunk, 0, torch.float32))
-        close(torch.cat(got), want, 1e-5, f"chunk {chunk} portions {sizes}")
+            qq = ops.qk_norm_rope_cache(dev(qkv)[at:at + n], None, None, None, None, b, kc, vc, 1, 1, dk, dv, 0, 1e-6, cdt)
+            got.append(ops.paged_attention_varlen(qq, kc, vc, b, 1, 1, dk, dv, bs, 1.0, chunk, 0, cdt))
+        close(torch.cat(got), want, tol, f"chunk {chunk} portions {sizes}")
+
+
+@pytest.mark.parametrize("chunk", [96, 64, 200, 33, 0])
+def test_tensor_core_attention_path(chunk):
+    """bf16 q / cache / out with 128-wide heads and 64-token blocks runs on the tensor-core kernel: random rows, grouped heads, scattered
+    blocks, two requests of unequal progress in one step"""
+    H, Gk, dk, bs, scale = 4, 2, 128, 64, 0.09
+    g = torch.Generator().manual_seed(chunk)
+    lens = (300, 131)
+    data, wants = [], []
+    for T in lens:
+        q, k, v = (torch.randn(T, n, dk, generator=g).to(torch.bfloat16).float() for n in (H, Gk, Gk))
+        data.append(torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], 1))
+        wants.append(G.masked_attention(q.to(F64), k.to(F64), v.to(F64), scale, dict(size=chunk) if chunk else None, torch.arange(T)).reshape(T, -1))
+    nb = 8
+    perm = list(np.random.default_rng(2).permutation(nb))
+    tables = [perm[:5], perm[5:]]
+    kc = torch.zeros((nb, bs, Gk, dk), device=DEV, dtype=torch.bfloat16); vc = torch.zeros_like(kc)
+    plans = [[70, 1, 1, 64, 100, 1, 63], [1, 2, 64, 1, 1, 30, 32]]
+    fed, got, step = [0, 0], [[], []], 0
+    while fed[0] < lens[0] or fed[1] < lens[1]:
+        ent, ns = [], []
+        for i in (0, 1):
+            n = min(plans[i][step % 7], lens[i] - fed[i])
+            ns.append(n)
+            if n:
+                ent.append(dict(tokens=[0] * n, start=fed[i], block_table=tables[i], state_slot=-1, want=[]))
+        b = batch_of(ent, bs)
+        rows = torch.cat([data[i][fed[i]:fed[i] + ns[i]] for i in (0, 1)])
+        qq = ops.qk_norm_rope_cache(dev(rows), None, None, None, None, b, kc, vc, H, Gk, dk, dk, 0, 1e-6, torch.bfloat16)
+        out = ops.paged_attention_varlen(qq, kc, vc, b, H, Gk, dk, dk, bs, scale, chunk, 0, torch.bfloat16)
+        at = 0
+        for i in (0, 1):
+            got[i].append(out[at:at + ns[i]]); at += ns[i]; fed[i] += ns[i]
+        step += 1
+    for i in (0, 1):
+        close(torch.cat(got[i]), wants[i], 1.5e-2, f"chunk {chunk} request {i}")
 
 
 def test_sliding_window_parameter():
@@ -248,6 +287,9 @@ CONFIGS = {
     "tiny": S.gobesun_config(40, 50, [S.gobesun_delta_layer(1, 1, 128, 32, conv=5), S.gobesun_attention_layer(1, 1, 40, 8, 64, 40, ff=48)],
                              loop=dict(start=0, stop=2, times=3)),
 }
+# attention heads of 128 with 64-token blocks: in bf16 this is the tensor-core attention path
+CONFIGS["wide"] = S.gobesun_config(64, 80, [S.gobesun_attention_layer(2, 1, 128, 128, 96, 64, scaling=YARN), S.gobesun_delta_layer(2, 1, 32, 32, conv=4, ff=96)],
+                                   loop=dict(start=0, stop=1, times=2))
 CONFIGS["plain"].pop("loop")
 _CACHE = {}
 
@@ -405,3 +447,27 @@ def test_sampling_with_temperature_is_seeded(tmp_path):
         eng = LLMEngine(model, num_blocks=4, max_num_seqs=2)
         outs.append(eng.generate([[1, 2, 3], [4, 5]], pkg.SamplingParams(temperature=0.9, top_k=12, top_p=0.9, max_tokens=8, seed=11)))
     assert outs[0] == outs[1] and all(0 <= t < cfg["vocab"] for o in outs[0] for t in o)
+
+
+def test_graph_replay_of_decode_steps_matches_eager():
+    """steps of single tokens through captured CUDA graphs (two batch sizes, growing tables) against the eager path and the oracle"""
+    cfg = CONFIGS["loop2"]
+    w = S.gobesun_weights(cfg, 0)
+    model = GobesunModel(GobesunConfig.from_dict(cfg), w, dtype=torch.float32, block_size=64, max_pos=64, device=DEV)      # tables must grow
+    g = torch.Generator().manual_seed(3)
+    seqs = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (100, 140)]
+    refs = [G.forward(cfg, w, s) for s in seqs]
+    runner = ModelRunner(model, 6, 2, 64, decode_graphs=True)
+    got = [[], []]
+    runner.admit(0); runner.admit(1)
+    out = runner.execute([dict(seq_id=0, tokens=seqs[0][:50], want=list(range(50))), dict(seq_id=1, tokens=seqs[1][:61], want=list(range(61)))])
+    got[0].append(out[:50]); got[1].append(out[50:])
+    fed = [50, 61]
+    while fed[0] < 100 or fed[1] < 140:
+        live = [i for i in (0, 1) if fed[i] < len(seqs[i])]
+        out = runner.execute([dict(seq_id=i, tokens=[seqs[i][fed[i]]], want=[0]) for i in live]).clone()
+        for r, i in enumerate(live):
+            got[i].append(out[r:r + 1]); fed[i] += 1
+    assert 1 in runner._graphs            # (the two-entry graph was dropped when the rotary tables grew, and captured again while needed)
+    for i in (0, 1):
+        close(torch.cat(got[i]), refs[i], TOL[torch.float32], f"graph replay, request {i}")
