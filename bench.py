@@ -49,6 +49,11 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--parity-steps", type=int, default=3, help="decode steps compared against a TP=1 engine before timing (0 = off)")
+    ap.add_argument("--arch", default="llama", choices=["llama", "gobesun"],
+                    help="llama = the metric (default, unchanged).  gobesun = prefill / decode throughput of the Gobesun decoder at layer sizes of real "
+                         "models (random weights), beside a dense bf16 Llama of equal width / heads / ff / depth, with a per-kernel roofline table; "
+                         "one JSON line, single GPU.")
+    ap.add_argument("--arch-sizes", default="w2048,w4096")
     return ap.parse_args()
 
 
@@ -616,8 +621,227 @@ def traffic_fields(world, B, esz):
     return {"traffic": t, "traffic_source": src} if t else {"traffic": None, "traffic_source": "no tracked ncu export found"}
 
 
+# ------------------------------------------------------------------------------------------------
+# --arch gobesun: the new decoder beside the closest existing model at equal size
+# ------------------------------------------------------------------------------------------------
+ARCH_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv=4, ff=5632, vocab=32000, layers=8, chunk=2048),
+    "w4096": dict(width=4096, heads=32, kv=8, ff=11008, vocab=32000, layers=4, chunk=2048),
+}
+
+
+def run_gobesun(args):
+    import torch
+    import candle_vllm_b200 as pkg
+    from candle_vllm_b200 import seq_ops as ops, synthetic as S
+    from candle_vllm_b200 import backend as BK
+    from candle_vllm_b200.engine import ModelRunner
+    from candle_vllm_b200.gobesun import GobesunConfig, GobesunModel
+    from candle_vllm_b200.inputs import prepare_prompt, to_device
+
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else \
+        {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+    HBM, TC = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    K, W = max(args.steps, 1), max(args.warmup, 3)
+    P, B, CTX, hd = 4096, 32, 1024, 128
+    bf = torch.bfloat16
+    l0 = pkg.lib().b200_total_kernel_launches()
+
+    def timed(fn, reps, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e-3            # seconds per call
+
+    sampler = ClockSampler(0); sampler.start()
+    results = {}
+    for name in [n for n in args.arch_sizes.split(",") if n in ARCH_SIZES]:
+        z = ARCH_SIZES[name]
+        D, H, G, ff, V, NL = z["width"], z["heads"], z["kv"], z["ff"], z["vocab"], z["layers"]
+        # ---- Gobesun: three recurrent layers to one attention layer, every layer with a feed-forward -------------------------------
+        layers = []
+        for i in range(NL):
+            layers.append(S.gobesun_attention_layer(H, G, hd, hd, z["chunk"], 64, ff=ff, base=1e6) if i % 4 == 3 else
+                          S.gobesun_delta_layer(H, H // 2, hd, hd, conv=4, ff=ff))
+        cfg = S.gobesun_config(D, V, layers)
+        model = GobesunModel(GobesunConfig.from_dict(cfg), S.gobesun_weights(cfg, 0), dtype=bf, block_size=64, max_pos=P + 64, device=dev)
+        blocks_per = -(-(CTX + K + W + 8) // 64)
+        runner = ModelRunner(model, B * blocks_per + P // 64 + 1, B + 1, 64, decode_graphs=True, max_blocks_per_seq=blocks_per)
+        toks = torch.randint(0, V, (P,), generator=torch.Generator().manual_seed(1)).tolist()
+
+        def g_prefill():
+            runner.admit(10 ** 6)
+            runner.execute([dict(seq_id=10 ** 6, tokens=toks, want=[P - 1])])
+            runner.release(10 ** 6)
+        g_pre = timed(g_prefill, 3, 2)
+        for i in range(B):
+            runner.admit(i)
+        for i in range(0, B, 4):
+            runner.execute([dict(seq_id=j, tokens=toks[:CTX], want=[]) for j in range(i, i + 4)])
+        step_entries = lambda: [dict(seq_id=j, tokens=[toks[j]], want=[0]) for j in range(B)]
+        g_dec = timed(lambda: runner.execute(step_entries()), K, W)          # host metadata + 2 H2D copies + graph replay, per step
+        g_dec_dev = timed(runner._graphs[B].graph.replay, K, 3)                  # the captured step alone (device time)
+        # ---- per-kernel times of the Gobesun step, from the model's own call sequence (eager, CUDA events around every op) ------
+        kern = {}
+        names = ["linear", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled", "causal_conv_silu", "gated_delta_rule", "gated_rms_norm",
+                 "qk_norm_rope_cache", "paged_attention_varlen", "paged_attention_decode_chunked"]
+        orig = {n: getattr(ops, n) for n in names}
+
+        def instrument(tag):
+            def wrap(n):
+                def f(*a, **k):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize(); e0.record()
+                    r = orig[n](*a, **k)
+                    e1.record(); torch.cuda.synchronize()
+                    key = n if n != "linear" else f"linear[{a[1].shape[0]}x{a[1].shape[1]}]"
+                    kern.setdefault((tag, key), []).append(e0.elapsed_time(e1) * 1e-3)
+                    return r
+                return f
+            for n in names:
+                setattr(ops, n, wrap(n))
+        instrument("prefill")
+        g_prefill(); kern.clear(); g_prefill()
+        runner.decode_graphs = False
+        instrument("decode")
+        runner.execute(step_entries())
+        for k in [k for k in kern if k[0] == "decode"]:
+            kern.pop(k)
+        runner.execute(step_entries())
+        for n in names:
+            setattr(ops, n, orig[n])
+        del runner, model
+        torch.cuda.empty_cache()
+
+        # ---- Llama of equal size ---------------------------------------------------------------------------------------------------
+        lcfg = pkg.LlamaConfig(hidden=D, num_layers=NL, num_heads=H, num_kv_heads=G, head_dim=hd, ffn=ff, vocab=V, rms_eps=1e-5, rope_theta=1e6,
+                               max_pos=P + 64, block_size=64, max_num_seqs=B, max_blocks_per_seq=blocks_per)
+        lw = S.make_weights_16bit(lcfg, dev, seed=0, dtype=bf)
+        nblk = max(B * blocks_per, P // 64 + 1)
+        eng = pkg.CacheEngine(NL, G, hd, pkg.CacheConfig(64, nblk), device=dev)
+        S.fill_kv_cache(eng.gpu_cache, seed=1)
+        lm = pkg.GGUFLLaMa(lcfg, lw, eng.gpu_cache, kv_dtype=pkg.DType.BF16, rope_neox=True)
+        tables = S.random_block_tables(B, blocks_per, nblk, seed=2)
+        prep = pkg.prepare_decode([CTX + 1] * B, toks[:B], tables, 64)
+        lm.decode(prep)
+        l_dec = timed(lambda: lm.decode_resident(B, advance=True), K, W)
+        # prefill: the same layer written with the framework's operators (the decode engine has no prompt path of its own)
+        lk = {}
+        pp = prepare_prompt([toks], [list(range(P // 64 + 1))], 64)
+        tok_d, pos_d, meta = to_device(pp, dev)
+        inv = 1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+        ang = torch.arange(P + 64, dtype=torch.float64)[:, None] * inv[None, :]
+        cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+        att = BK.PagedAttention(H, hd, hd ** -0.5, G)
+        lin = {k: [BK.Linear(l[k]) for l in lw["layers"]] for k in ("wq", "wk", "wv", "wo", "w1", "w2", "w3")}
+        lin_out = BK.Linear(lw["output"])
+        emb = lw["tok_embeddings"]
+
+        def op(key, fn, rec):
+            if not rec:
+                return fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(); e0.record()
+            r = fn()
+            e1.record(); torch.cuda.synchronize()
+            lk.setdefault(key, []).append(e0.elapsed_time(e1) * 1e-3)
+            return r
+
+        def l_prefill(rec=False):
+            x = emb[tok_d]
+            for i, l in enumerate(lw["layers"]):
+                h = op("rms_norm", lambda: BK.rms_norm(x, l["attn_norm"], 1e-5, bf), rec)
+                q = op(f"linear[{H * hd}x{D}]", lambda: lin["wq"][i].forward(h), rec)
+                k = lin["wk"][i].forward(h); v = lin["wv"][i].forward(h)
+                qf, kf = q.float().view(P, H, hd), k.float().view(P, G, hd)
+                op("fused_rope", lambda: BK.fused_rope(qf, kf, cos, sin, pos_d, False), rec)
+                kc, vc = eng.gpu_cache[i]
+                qb, kb = qf.to(bf), kf.to(bf)
+                op("reshape_and_cache", lambda: BK.reshape_and_cache(kb, v.view(P, G, hd), kc, vc, meta.slot_mapping), rec)
+                a = op("paged_attention_prefill", lambda: att.forward(qb, None, None, None, kc, vc, meta), rec)
+                x = x + lin["wo"][i].forward(a.view(P, H * hd)).float()
+                h = BK.rms_norm(x, l["ffn_norm"], 1e-5, bf)
+                g1 = op(f"linear[{ff}x{D}]", lambda: lin["w1"][i].forward(h), rec)
+                u = lin["w3"][i].forward(h)
+                m = op("silu_mul", lambda: BK.silu_mul(g1.float(), u.float(), torch.float32), rec).to(bf)
+                x = x + op(f"linear[{D}x{ff}]", lambda: lin["w2"][i].forward(m), rec).float()
+            return lin_out.forward(BK.rms_norm(x[-1:], lw["norm"], 1e-5, bf))
+        l_pre = timed(l_prefill, 3, 2)
+        l_prefill(True); lk.clear(); l_prefill(True)
+        del lm, eng, lw, lin, lin_out
+        torch.cuda.empty_cache()
+
+        med = lambda v: sorted(v)[len(v) // 2]
+        esz = 2
+        Gd = H // 2                                    # key heads of the recurrent layers
+        Cd = 2 * Gd * hd + H * hd
+        # algorithmic work per call: ("bytes", n) is set against the measured copy bandwidth, ("flops", n) against the measured bf16 GEMM rate
+        def work(tag, key, T):
+            if key.startswith("linear["):
+                n, k = (int(v) for v in key[7:-1].split("x"))
+                return ("flops", 2.0 * T * n * k) if tag == "prefill" else ("bytes", n * k * esz + T * (k * esz + n * 4))
+            return {
+                "rms_norm_ex": ("bytes", T * D * (4 + esz)), "rms_norm": ("bytes", T * D * (4 + esz)),
+                "gelu_tanh_mul": ("bytes", T * ff * (8 + esz)), "silu_mul": ("bytes", T * ff * (8 + esz)),
+                "embedding_scaled": ("bytes", T * D * (esz + 4)),
+                "causal_conv_silu": ("bytes", T * Cd * 8),
+                "gated_rms_norm": ("bytes", T * H * hd * (8 + esz)),
+                "qk_norm_rope_cache": ("bytes", T * ((H + 2 * G) * hd * 4 + H * hd * esz + 2 * G * hd * esz)),
+                "fused_rope": ("bytes", T * (H + G) * hd * 8), "reshape_and_cache": ("bytes", T * 2 * G * hd * esz * 2),
+                # recurrence: q, k, v in and o out (f32) plus one read and one write of every entry's state
+                "gated_delta_rule": ("bytes", T * (Cd + H * hd) * 4 + (1 if tag == "prefill" else T) * 2 * H * hd * hd * 4),
+                # causal attention inside chunks of `chunk` keys
+                "paged_attention_varlen": ("flops", 4.0 * H * hd * sum(min(i % z["chunk"] + 1, i + 1) for i in range(T))) if tag == "prefill"
+                else ("bytes", T * (min(CTX, CTX % z["chunk"] + 1)) * 2 * G * hd * esz),
+                "paged_attention_decode_chunked": ("bytes", T * (min(CTX, CTX % z["chunk"] + 1)) * 2 * G * hd * esz),
+                "paged_attention_prefill": ("flops", 4.0 * H * hd * T * (T + 1) / 2),
+            }.get(key)
+
+        def table(rows, tag, T):
+            out = {}
+            for key, v in rows:
+                w = work(tag, key, T)
+                t = med(v)
+                e = {"us": round(t * 1e6, 1), "calls_per_step": len(v)}
+                if w:
+                    roof = w[1] / (HBM if w[0] == "bytes" else TC)
+                    e.update(bound=w[0], roofline_us=round(roof * 1e6, 2), frac_of_measured_peak=round(roof / t, 3))
+                out[key] = e
+            return out
+        results[name] = {
+            "gobesun": {"prefill_tokens_per_s": round(P / g_pre), "prefill_ms": round(g_pre * 1e3, 2), "decode_tokens_per_s": round(B / g_dec),
+                        "decode_ms_per_step": round(g_dec * 1e3, 3), "decode": "CUDA-graph replay incl. host metadata and H2D",
+                        "decode_ms_per_step_device": round(g_dec_dev * 1e3, 3), "decode_tokens_per_s_device": round(B / g_dec_dev),
+                        "kernels_prefill": table([(k[1], v) for k, v in kern.items() if k[0] == "prefill"], "prefill", P),
+                        "kernels_decode": table([(k[1], v) for k, v in kern.items() if k[0] == "decode"], "decode", B)},
+            "llama_dense_bf16": {"prefill_tokens_per_s": round(P / l_pre), "prefill_ms": round(l_pre * 1e3, 2), "decode_tokens_per_s": round(B / l_dec),
+                                 "decode_ms_per_step": round(l_dec * 1e3, 3), "decode": "CUDA-graph replay, device-resident metadata",
+                                 "prefill": "layer written with the framework's operators (f32 glue through torch)",
+                                 "kernels_prefill": table(list(lk.items()), "prefill", P)},
+            "shape": dict(z, prompt=P, decode_batch=B, decode_ctx=CTX, head_dim=hd),
+        }
+    clocks = sampler.stop()
+    first = results[next(iter(results))]
+    print(json.dumps({"metric": "Gobesun prefill / decode tokens/s beside dense bf16 Llama of equal size", "value": first["gobesun"]["decode_tokens_per_s"],
+                      "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "arch": "gobesun",
+                      "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "source": "fallback" if peaks.get("fallback") else "MEASURED_PEAKS.json"},
+                      "l2": "weights and activations of a step exceed L2 (126 MB)", "clocks": clocks,
+                      "gpu_launches": int(pkg.lib().b200_total_kernel_launches() - l0), "sizes": results}))
+
+
 def main():
     args = parse()
+    if args.arch == "gobesun":
+        run_gobesun(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -34,7 +34,8 @@ def _newer(target: str, deps) -> bool:
 # Source groups that link into a library of their own: what one model family needs, so that a first start from a source-only checkout
 # compiles that and nothing else.  "ragged" = the ragged-step decoders (seq_ops.py): error state, both linear kernels, norms /
 # activations, recurrent and attention mixers, argmax.
-GROUPS = {"ragged": ["lib", "linear_generic", "dense_gemm", "norm_act", "gated_delta", "attention_varlen", "attention_prefill", "elementwise"]}
+GROUPS = {"ragged": ["lib", "linear_generic", "dense_gemm", "norm_act", "gated_delta", "attention_varlen", "attention_prefill", "attention_decode", "attention_generic",
+                     "attention_api", "elementwise"]}
 
 
 def so_path(group=None) -> str:

@@ -67,6 +67,21 @@ qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float
         for (int i = threadIdx.x; i < nv; i += 256) v_cache[slot * nv + i] = from_f32<TC>(row[nq + nk + i]);
 }
 
+// Steps made of single tokens: a query at position i sees the keys chunk_start .. i with chunk_start = floor(i / chunk) * chunk.  When
+// chunks start on block borders that is an ordinary decode over a context of i - chunk_start + 1 keys whose block table is the
+// sequence's table moved left by chunk_start / block_size blocks -- so the split-KV decode kernel of the other models serves it.
+__global__ void chunk_decode_view_kernel(const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ positions,
+                                         uint32_t* __restrict__ out_tables, uint32_t* __restrict__ out_ctx, int num_seqs, int out_width,
+                                         int block_size, int chunk) {
+    const int b = blockIdx.x;
+    const int pos = positions[b];
+    const int cs = (pos / chunk) * chunk;
+    const int first = cs / block_size;
+    if (threadIdx.x == 0) out_ctx[b] = (uint32_t)(pos - cs + 1);
+    for (int j = threadIdx.x; j < out_width; j += blockDim.x)
+        out_tables[(int64_t)b * out_width + j] = first + j < table_width ? (uint32_t)block_tables[(int64_t)b * table_width + first + j] : 0u;
+}
+
 constexpr int kMaxVPerLane = 8;      // value size <= 256
 
 template <typename TC, typename TOut, typename TQ>
@@ -161,6 +176,17 @@ void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, con
 #undef QNRC
     count_launch();
     check_launch("qk_norm_rope_cache");
+}
+
+void chunk_decode_view(const int32_t* block_tables, int32_t table_width, const int32_t* positions, uint32_t* out_tables, uint32_t* out_ctx,
+                       int32_t num_seqs, int32_t out_width, int32_t block_size, int32_t chunk, int64_t stream) {
+    if (num_seqs == 0) return;
+    B200_REQUIRE(block_tables && positions && out_tables && out_ctx && table_width > 0 && out_width > 0 && block_size > 0 && chunk > 0 &&
+                 chunk % block_size == 0, kErrBadArg, "chunk_decode_view: bad arguments (chunk must be a multiple of the block size)");
+    chunk_decode_view_kernel<<<num_seqs, 64, 0, as_stream(stream)>>>(block_tables, table_width, positions, out_tables, out_ctx, num_seqs, out_width,
+                                                                     block_size, chunk);
+    count_launch();
+    check_launch("chunk_decode_view");
 }
 
 void paged_attention_varlen(void* out, const void* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,

@@ -11,10 +11,10 @@
 //                           what that kernel reads).
 //   gated_delta_rule        per head, S [dk, dv]:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                           with q, k made unit vectors (q also times dk^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) *
-//                           softplus(a + dt_bias)).  One warp owns 32 value columns of one head of one entry and walks the
-//                           portion token by token with its slice of S in registers (dk <= 128) or shared memory; the next
-//                           token's operands are fetched while the current one is applied.  Decode (one token per entry) is
-//                           one read and one write of the state.
+//                           softplus(a + dt_bias)).  A block owns 32 value columns of one head of one entry with its slice of S in
+//                           registers and walks the portion in tiles of 16 tokens staged through shared memory, the next
+//                           tile in flight while the current one is applied.  Decode (one token per entry) is one read and
+//                           one write of the state.
 //   gated_rms_norm          out = o / rms(o over dv) * w * silu(gate), per (token, head).
 #include "common.cuh"
 
@@ -67,94 +67,133 @@ causal_conv_update_kernel(const float* __restrict__ x, int64_t ldx, float* __res
     }
 }
 
-// kDK > 0: dk == kDK, state slice in registers.  kDK == 0: any dk <= 256, state slice in shared memory [dk][32].
-template <int kDK>
-__global__ void __launch_bounds__(32)
+// A block of four warps owns 32 value columns of one head of one entry (8 per warp); inside a warp the key rows are split four ways
+// (lane = 8 * part + column, part p holds rows p * kR .. p * kR + kR - 1 of its column in registers), so a token costs kR multiply-adds
+// per lane per pass instead of dk and two butterfly steps join the four partial sums.  kR = rows per part (dk <= 4 * kR; rows past dk are
+// zero and stay zero).  Tokens are taken in tiles of 16: the block loads the NEXT tile's q, k, v, a, b into registers (coalesced, all in
+// flight at once) while it walks the current tile out of shared memory, where q and k were made unit vectors and beta / decay were
+// worked out for all 16 tokens in parallel -- the serial part of a token is then two short multiply-add chains and two butterflies.
+// Every sum has a fixed order, so portions of any size give the same state bit for bit.
+constexpr int kTile = 16;
+
+template <int kR>
+__global__ void __launch_bounds__(128)
 gated_delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__ proj, int64_t ld_proj, int off_b, int off_a,
                         const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ state, float* __restrict__ out,
                         const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ seq_slots, const int32_t* __restrict__ seq_start,
-                        int H, int G, int dk_rt, int dv) {
-    extern __shared__ float smem[];
-    const int dk = kDK > 0 ? kDK : dk_rt;
-    constexpr int kPer = kDK > 0 ? (kDK + 31) / 32 : 8;       // q / k elements a lane stages per token
-    float* ks = smem;                 // [dk] unit key of the current token
-    float* qs = smem + dk;            // [dk] scaled unit query
-    float* Ss = smem + 2 * dk;        // [dk][32] when kDK == 0
-    const int lane = threadIdx.x;
+                        int H, int G, int dk, int dv) {
+    constexpr int kDP = 4 * kR;                       // padded key size
+    constexpr int kNQ = kTile * kDP / 128;            // q (and k) elements a thread stages per tile
+    extern __shared__ float sm[];
+    float* qs = sm;                                   // [kTile][kDP]
+    float* ks = qs + kTile * kDP;                     // [kTile][kDP]
+    float* vs = ks + kTile * kDP;                     // [kTile][32]
+    float* bs = vs + kTile * 32;                      // [kTile] b, then beta
+    float* ds = bs + kTile;                           // [kTile] a, then decay
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, part = lane >> 3;
     const int b = blockIdx.z, h = blockIdx.y;
-    const int col = blockIdx.x * 32 + lane;
+    const int col = blockIdx.x * 32 + warp * 8 + (lane & 7);
     const bool live = col < dv;
     const int g = h / (H / G);
     const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
     if (n <= 0) return;
     const int C = 2 * G * dk + H * dv;
-    float* Sg = state + (((int64_t)seq_slots[b] * H + h) * dk) * dv + col;
+    const int row0 = part * kR;
+    float* Sg = state + (((int64_t)seq_slots[b] * H + h) * dk + row0) * dv + col;
     const bool fresh = seq_start[b] == 0;
-    float S[kDK > 0 ? kDK : 1];
-    if constexpr (kDK > 0) {
+    float S[kR];
 #pragma unroll
-        for (int i = 0; i < kDK; ++i) S[i] = (live && !fresh) ? Sg[(int64_t)i * dv] : 0.f;
-    } else {
-        for (int i = 0; i < dk; ++i) Ss[i * 32 + lane] = (live && !fresh) ? Sg[(int64_t)i * dv] : 0.f;
-    }
+    for (int r = 0; r < kR; ++r) S[r] = (live && !fresh && row0 + r < dk) ? Sg[(int64_t)r * dv] : 0.f;
     const float neg_rate = -expf(A_log[h]);
     const float bias = dt_bias[h];
     const float qscale = 1.0f / sqrtf((float)dk);
 
-    float kr[kPer], qr[kPer], vr, ar, br;
-    auto fetch = [&](int t) {
-        const float* row = qkv + (int64_t)t * C;
+    float rq[kNQ], rk[kNQ], rv[kTile * 32 / 128], ra = 0.f, rb = 0.f;
+    auto load_tile = [&](int first, int cnt) {        // global -> registers
 #pragma unroll
-        for (int e = 0; e < kPer; ++e) {
-            const int i = lane + 32 * e;
-            qr[e] = i < dk ? row[g * dk + i] : 0.f;
-            kr[e] = i < dk ? row[G * dk + g * dk + i] : 0.f;
+        for (int j = 0; j < kNQ; ++j) {
+            const int e = tid + 128 * j, tt = e / kDP, i = e - tt * kDP;
+            const bool in = tt < cnt && i < dk;
+            const float* row = qkv + (int64_t)(first + tt) * C + g * dk + i;
+            rq[j] = in ? row[0] : 0.f;
+            rk[j] = in ? row[G * dk] : 0.f;
         }
-        vr = live ? row[2 * G * dk + h * dv + col] : 0.f;
-        br = proj[(int64_t)t * ld_proj + off_b + h];
-        ar = proj[(int64_t)t * ld_proj + off_a + h];
+#pragma unroll
+        for (int j = 0; j < kTile * 32 / 128; ++j) {
+            const int e = tid + 128 * j, tt = e >> 5, c = blockIdx.x * 32 + (e & 31);
+            rv[j] = (tt < cnt && c < dv) ? qkv[(int64_t)(first + tt) * C + 2 * G * dk + h * dv + c] : 0.f;
+        }
+        if (tid < kTile && tid < cnt) {
+            rb = proj[(int64_t)(first + tid) * ld_proj + off_b + h];
+            ra = proj[(int64_t)(first + tid) * ld_proj + off_a + h];
+        }
     };
-    fetch(t0);
-    for (int s = 0; s < n; ++s) {
-        const int t = t0 + s;
-        // unit vectors (32-bit), staged for broadcast
-        float qq = 0.f, kk = 0.f;
+    auto store_tile = [&]() {                          // registers -> shared memory
 #pragma unroll
-        for (int e = 0; e < kPer; ++e) { qq = fmaf(qr[e], qr[e], qq); kk = fmaf(kr[e], kr[e], kk); }
-        qq = warp_sum(qq); kk = warp_sum(kk);
-        const float qn = qscale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
-        __syncwarp();
+        for (int j = 0; j < kNQ; ++j) { qs[tid + 128 * j] = rq[j]; ks[tid + 128 * j] = rk[j]; }
 #pragma unroll
-        for (int e = 0; e < kPer; ++e) {
-            const int i = lane + 32 * e;
-            if (i < dk) { qs[i] = qr[e] * qn; ks[i] = kr[e] * kn; }
+        for (int j = 0; j < kTile * 32 / 128; ++j) vs[tid + 128 * j] = rv[j];
+        if (tid < kTile) { bs[tid] = rb; ds[tid] = ra; }
+    };
+    auto prepare_tile = [&](int cnt) {                 // unit vectors, beta, decay: 4 tokens per warp, in parallel
+        for (int tt = warp; tt < cnt; tt += 4) {
+            float qq = 0.f, kk = 0.f;
+            for (int i = lane; i < kDP; i += 32) { const float a = qs[tt * kDP + i], c = ks[tt * kDP + i]; qq = fmaf(a, a, qq); kk = fmaf(c, c, kk); }
+            qq = warp_sum(qq); kk = warp_sum(kk);
+            const float qn = qscale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
+            for (int i = lane; i < kDP; i += 32) { qs[tt * kDP + i] *= qn; ks[tt * kDP + i] *= kn; }
+            if (lane == 0) {
+                bs[tt] = 1.0f / (1.0f + expf(-bs[tt]));
+                ds[tt] = expf(neg_rate * softplus_f(ds[tt] + bias));
+            }
         }
-        const float v = vr;
-        const float beta = 1.0f / (1.0f + expf(-br));
-        const float decay = expf(neg_rate * softplus_f(ar + bias));
-        __syncwarp();
-        if (s + 1 < n) fetch(t + 1);
-        float pred = 0.f, o = 0.f;
-        if constexpr (kDK > 0) {
+    };
+    auto join4 = [](float v) {                         // sum over the four parts (lanes that differ in bits 3 and 4)
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        return v;
+    };
+
+    const int tiles = (n + kTile - 1) / kTile;
+    load_tile(t0, min(kTile, n));
+    for (int tile = 0; tile < tiles; ++tile) {
+        const int first = t0 + tile * kTile, cnt = min(kTile, n - tile * kTile);
+        __syncthreads();                               // every warp has finished the previous tile
+        store_tile();
+        __syncthreads();
+        prepare_tile(cnt);
+        __syncthreads();
+        if (tile + 1 < tiles) load_tile(first + kTile, min(kTile, n - (tile + 1) * kTile));
+        for (int tt = 0; tt < cnt; ++tt) {
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tt * kDP + row0);
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tt * kDP + row0);
+            const float decay = ds[tt], beta = bs[tt], v = vs[tt * 32 + warp * 8 + (lane & 7)];
+            float kd[kR];
+            float p[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < kDK; ++i) { S[i] *= decay; pred = fmaf(S[i], ks[i], pred); }
+            for (int r = 0; r < kR; r += 4) {
+                const float4 c = k4[r >> 2];
+                kd[r] = c.x; kd[r + 1] = c.y; kd[r + 2] = c.z; kd[r + 3] = c.w;
+                S[r] *= decay; S[r + 1] *= decay; S[r + 2] *= decay; S[r + 3] *= decay;
+                p[0] = fmaf(S[r], c.x, p[0]); p[1] = fmaf(S[r + 1], c.y, p[1]); p[2] = fmaf(S[r + 2], c.z, p[2]); p[3] = fmaf(S[r + 3], c.w, p[3]);
+            }
+            const float pred = join4((p[0] + p[1]) + (p[2] + p[3]));
             const float u = beta * (v - pred);
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < kDK; ++i) { S[i] = fmaf(ks[i], u, S[i]); o = fmaf(S[i], qs[i], o); }
-        } else {
-            for (int i = 0; i < dk; ++i) { const float sv = Ss[i * 32 + lane] * decay; Ss[i * 32 + lane] = sv; pred = fmaf(sv, ks[i], pred); }
-            const float u = beta * (v - pred);
-            for (int i = 0; i < dk; ++i) { const float sv = fmaf(ks[i], u, Ss[i * 32 + lane]); Ss[i * 32 + lane] = sv; o = fmaf(sv, qs[i], o); }
+            for (int r = 0; r < kR; r += 4) {
+                const float4 a = q4[r >> 2];
+                S[r] = fmaf(kd[r], u, S[r]); S[r + 1] = fmaf(kd[r + 1], u, S[r + 1]); S[r + 2] = fmaf(kd[r + 2], u, S[r + 2]); S[r + 3] = fmaf(kd[r + 3], u, S[r + 3]);
+                o[0] = fmaf(S[r], a.x, o[0]); o[1] = fmaf(S[r + 1], a.y, o[1]); o[2] = fmaf(S[r + 2], a.z, o[2]); o[3] = fmaf(S[r + 3], a.w, o[3]);
+            }
+            const float ov = join4((o[0] + o[1]) + (o[2] + o[3]));
+            if (live && part == 0) out[(int64_t)(first + tt) * H * dv + h * dv + col] = ov;
         }
-        if (live) out[(int64_t)t * H * dv + h * dv + col] = o;
     }
     if (live) {
-        if constexpr (kDK > 0) {
 #pragma unroll
-            for (int i = 0; i < kDK; ++i) Sg[(int64_t)i * dv] = S[i];
-        } else {
-            for (int i = 0; i < dk; ++i) Sg[(int64_t)i * dv] = Ss[i * 32 + lane];
-        }
+        for (int r = 0; r < kR; ++r)
+            if (row0 + r < dk) Sg[(int64_t)r * dv] = S[r];
     }
 }
 
@@ -211,12 +250,15 @@ void gated_delta_rule(const float* qkv, const float* proj, int64_t ld_proj, int3
     B200_REQUIRE(dk <= 256, kErrUnsupported, "gated_delta_rule: key size %d > 256", dk);
     cudaStream_t st = as_stream(stream);
     const dim3 grid(ceil_div(dv, 32), num_heads, num_seqs);
-#define GDR(DK, SMEM) gated_delta_rule_kernel<DK><<<grid, 32, (SMEM), st>>>(qkv, proj, ld_proj, off_b, off_a, A_log, dt_bias, state, out, cu_seqlens, \
-                                                                          seq_slots, seq_start, num_heads, num_kv_heads, dk, dv)
-    if (dk == 32) GDR(32, 2 * 32 * 4);
-    else if (dk == 64) GDR(64, 2 * 64 * 4);
-    else if (dk == 128) GDR(128, 2 * 128 * 4);
-    else GDR(0, (2 * dk + 32 * dk) * 4);
+#define GDR(R) do { \
+        const int smem = (2 * kTile * 4 * R + kTile * 32 + 2 * kTile) * (int)sizeof(float); \
+        ensure_dynamic_smem(reinterpret_cast<const void*>(gated_delta_rule_kernel<R>), smem); \
+        gated_delta_rule_kernel<R><<<grid, 128, smem, st>>>(qkv, proj, ld_proj, off_b, off_a, A_log, dt_bias, state, out, cu_seqlens, seq_slots, \
+                                                            seq_start, num_heads, num_kv_heads, dk, dv); } while (0)
+    if (dk <= 32) GDR(8);
+    else if (dk <= 64) GDR(16);
+    else if (dk <= 128) GDR(32);
+    else GDR(64);
 #undef GDR
     count_launch();
     check_launch("gated_delta_rule");

@@ -33,15 +33,16 @@ class _DecodeGraph:
         dev = runner.model.device
         self.B, self.W = B, width
         n = B * (4 + width) + B + 1
-        self.host = torch.zeros(n, dtype=torch.int32).pin_memory()
-        self.host_slots = torch.zeros(B, dtype=torch.int64).pin_memory()
+        # two pinned staging sets used in turn: a set is rewritten only after the copy that last read it has run on the device
+        self.stage = [(torch.zeros(n, dtype=torch.int32).pin_memory(), torch.zeros(B, dtype=torch.int64).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+        self.turn = 0
         self.meta = torch.zeros(n, dtype=torch.int32, device=dev)
         m = self.meta
         ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
         self.batch = StepBatch(tokens=m[0:B], positions=m[B:2 * B], token_seq=ar[:B].clone(), slot_mapping=torch.full((B,), -1, dtype=torch.int64, device=dev),
                                cu_seqlens=ar, cu_seqlens_k=m[4 * B + B * width:], seq_slots=m[2 * B:3 * B], seq_start=m[3 * B:4 * B],
                                block_tables=m[4 * B:4 * B + B * width].view(B, width),
-                               want_rows=ar[:B].clone(), num_tokens=B, num_seqs=B, num_want=B, max_position=0)
+                               want_rows=ar[:B].clone(), num_tokens=B, num_seqs=B, num_want=B, max_position=0, pure_decode=True)
         self.meta[2 * B:3 * B] = runner.state.scratch_slot
         self.meta[4 * B + B * width:] = ar                     # warm-up: one key per entry
         kv = runner.cache.gpu_cache if runner.cache else []
@@ -56,15 +57,19 @@ class _DecodeGraph:
             self.logits = runner.model.forward(self.batch, kv, runner.state.tensors)
 
     def replay(self, prep: dict) -> torch.Tensor:
-        B, h = self.B, self.host.numpy()
+        host, host_slots, copied = self.stage[self.turn]
+        self.turn ^= 1
+        copied.synchronize()
+        B, h = self.B, host.numpy()
         h[0:B], h[B:2 * B], h[2 * B:3 * B], h[3 * B:4 * B] = prep["tokens"], prep["positions"], prep["seq_slots"], prep["seq_start"]
         bt = prep["block_tables"]
         tab = h[4 * B:4 * B + B * self.W].reshape(B, self.W)
         tab[:, :bt.shape[1]] = bt
         h[4 * B + B * self.W:] = prep["cu_seqlens_k"]
-        self.host_slots.numpy()[:] = prep["slot_mapping"]
-        self.meta.copy_(self.host, non_blocking=True)
-        self.batch.slot_mapping.copy_(self.host_slots, non_blocking=True)
+        host_slots.numpy()[:] = prep["slot_mapping"]
+        self.meta.copy_(host, non_blocking=True)
+        self.batch.slot_mapping.copy_(host_slots, non_blocking=True)
+        copied.record()
         self.graph.replay()
         return self.logits
 

@@ -95,6 +95,9 @@ class PagedAttentionMixer:
             raise BackendError(f"PagedAttentionMixer: {self.rot_dims} rotary dims do not fit a head of {dk}")
         # 16-bit q for the tensor-core attention kernel (128-wide heads, 64-token blocks, bf16 cache); f32 q for the SIMT one
         self.q_dtype = torch.bfloat16 if (dtype == torch.bfloat16 and dk == dv == 128 and block_size == 64) else torch.float32
+        # steps of single tokens: the split-KV decode kernel, when chunks start on block borders and the head layout is one it takes
+        self.decode_kernel = (self.q_dtype == torch.bfloat16 and self.chunk > 0 and self.chunk % block_size == 0 and heads // kv_heads in (1, 2, 4, 8))
+        self._scratch = {}
         self.cos = self.sin = None
         self._device = self.w_in.device
         if rot:
@@ -114,8 +117,11 @@ class PagedAttentionMixer:
         proj = ops.linear(h, self.w_in)
         q = ops.qk_norm_rope_cache(proj, self.q_norm, self.k_norm, self.cos, self.sin, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dv,
                                    self.rot_dims, self.eps, self.q_dtype)
-        a = ops.paged_attention_varlen(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.dv, self.block_size, self.scale, self.chunk,
-                                       self.window, self.dtype)
+        if self.decode_kernel and batch.pure_decode and batch.num_seqs <= 256:
+            a = ops.paged_attention_decode_chunked(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.block_size, self.scale, self.chunk, self._scratch)
+        else:
+            a = ops.paged_attention_varlen(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.dv, self.block_size, self.scale, self.chunk,
+                                           self.window, self.dtype)
         return ops.linear(a, self.w_o)
 
 

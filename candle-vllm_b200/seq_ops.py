@@ -44,6 +44,7 @@ class StepBatch:
     num_seqs: int = 0
     num_want: int = 0
     max_position: int = 0
+    pure_decode: bool = False     # every entry brings exactly one token
 
     @classmethod
     def from_host(cls, prep: dict, device="cuda") -> "StepBatch":
@@ -53,7 +54,7 @@ class StepBatch:
                    seq_slots=t(prep["seq_slots"], np.int32), seq_start=t(prep["seq_start"], np.int32),
                    block_tables=t(prep["block_tables"], np.int32), want_rows=t(prep["want_rows"], np.int32),
                    num_tokens=len(prep["tokens"]), num_seqs=len(prep["seq_slots"]), num_want=len(prep["want_rows"]),
-                   max_position=int(prep["max_position"]))
+                   max_position=int(prep["max_position"]), pure_decode=len(prep["tokens"]) == len(prep["seq_slots"]))
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -165,4 +166,29 @@ def paged_attention_varlen(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
                                  C.c_int32(chunk), C.c_int32(window), C.c_int32(_tag(q.dtype)), C.c_int32(_tag(k_cache.dtype)), C.c_int32(_tag(out_dtype)),
                                  _stream(q.device))
     check("paged_attention_varlen")
+    return out
+
+
+def paged_attention_decode_chunked(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: StepBatch, heads: int, kv_heads: int, hd: int,
+                                   block_size: int, scale: float, chunk: int, scratch: dict) -> torch.Tensor:
+    """A step of single tokens under a chunk mask with chunk % block_size == 0, on the split-KV decode kernel of ``PagedAttention``: the
+    block tables are viewed from each sequence's chunk start (``chunk_decode_view``).  q bf16 [B, H * hd]; ``scratch`` keeps the view
+    and the kernel's workspace between calls (allocated on first use, so call once before capturing a graph)."""
+    B = q.shape[0]
+    width = chunk // block_size
+    key = (B, width)
+    if key not in scratch:
+        need = lib().paged_attention_decode_workspace_bytes(C.c_int32(B), C.c_int32(heads), C.c_int32(hd), C.c_int32(width), C.c_int32(block_size))
+        scratch[key] = (torch.zeros((B, width), dtype=torch.int32, device=q.device), torch.zeros(B, dtype=torch.int32, device=q.device),
+                        torch.zeros(int(need), dtype=torch.uint8, device=q.device))
+    tables, ctx, ws = scratch[key]
+    out = torch.empty((B, heads * hd), dtype=q.dtype, device=q.device)
+    L = lib()
+    L.chunk_decode_view(_ptr(batch.block_tables), C.c_int32(batch.block_tables.shape[1]), _ptr(batch.positions), _ptr(tables), _ptr(ctx), C.c_int32(B),
+                        C.c_int32(width), C.c_int32(block_size), C.c_int32(chunk), _stream(q.device))
+    L.paged_attention_decode(_ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(tables), _ptr(ctx), C.c_int32(B), C.c_int32(heads), C.c_int32(kv_heads),
+                             C.c_int32(hd), C.c_int32(block_size), C.c_int32(width), C.c_int64(k_cache.shape[0]), C.c_float(scale), C.c_float(0.0),
+                             C.c_int32(0), C.c_int32(_tag(q.dtype)), C.c_int32(_tag(k_cache.dtype)), C.c_int32(0), C.c_int32(_tag(q.dtype)), _ptr(ws),
+                             C.c_size_t(ws.numel()), _stream(q.device))
+    check("paged_attention_decode_chunked")
     return out

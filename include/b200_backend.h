@@ -447,6 +447,11 @@ void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, con
                         int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, void* q_out, void* key_cache, void* value_cache,
                         int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,
                         int32_t cache_dtype, int32_t q_dtype, int64_t stream);
+/* chunk_decode_view: for steps of single tokens under a chunk mask whose chunks start on block borders (chunk % block_size == 0): out_ctx[b] =
+ * positions[b] - chunk_start + 1 and out_tables[b] (u32 [num_seqs, out_width]) = the sequence's table from block chunk_start / block_size on,
+ * i.e. the (block_tables, context_lens) pair that makes paged_attention_decode attend to exactly the visible keys. */
+void chunk_decode_view(const int32_t* block_tables, int32_t table_width, const int32_t* positions, uint32_t* out_tables, uint32_t* out_ctx,
+                       int32_t num_seqs, int32_t out_width, int32_t block_size, int32_t chunk, int64_t stream);
 void paged_attention_varlen(void* out, const void* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,
                             int32_t table_width, const int32_t* token_seq, const int32_t* positions, const int32_t* cu_seqlens_q,
                             const int32_t* cu_seqlens_k, int32_t num_seqs, int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk,

@@ -290,6 +290,9 @@ CONFIGS = {
 # attention heads of 128 with 64-token blocks: in bf16 this is the tensor-core attention path
 CONFIGS["wide"] = S.gobesun_config(64, 80, [S.gobesun_attention_layer(2, 1, 128, 128, 96, 64, scaling=YARN), S.gobesun_delta_layer(2, 1, 32, 32, conv=4, ff=96)],
                                    loop=dict(start=0, stop=1, times=2))
+# the same with chunks that start on block borders: single-token steps in bf16 then run on the split-KV decode kernel
+CONFIGS["wide64"] = S.gobesun_config(64, 80, [S.gobesun_delta_layer(2, 2, 64, 16, conv=3), S.gobesun_attention_layer(4, 2, 128, 128, 128, 32, ff=96)],
+                                     loop=dict(start=1, stop=2, times=2))
 CONFIGS["plain"].pop("loop")
 _CACHE = {}
 
@@ -352,6 +355,31 @@ def test_portions_in_bf16_stay_within_rounding():
     parts = run_schedule(runner, 1, toks, [37, 2, 1, 1, 64])
     close(parts, ref, TOL[torch.bfloat16], "bf16 portions")
     close(parts, whole, 3e-2, "bf16 portions against the whole prompt")
+
+
+@pytest.mark.parametrize("name", ["wide", "wide64"])
+def test_bf16_decoding_on_the_tensor_core_attention_paths(name):
+    """128-wide heads in bf16: prompt portions and mixed steps use the tensor-core prefill kernel, steps of single tokens the split-KV
+    decode kernel when chunks start on block borders; two requests decode side by side across chunk and block edges"""
+    cfg = CONFIGS[name]
+    w = S.gobesun_weights(cfg, 0)
+    model = GobesunModel(GobesunConfig.from_dict(cfg), w, dtype=torch.bfloat16, block_size=64, max_pos=512, device=DEV)
+    g = torch.Generator().manual_seed(5)
+    seqs = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (300, 270)]
+    refs = [G.forward(cfg, w, s) for s in seqs]
+    runner = ModelRunner(model, 10, 2, 64)
+    runner.admit(0); runner.admit(1)
+    got = [[], []]
+    out = runner.execute([dict(seq_id=0, tokens=seqs[0][:100], want=list(range(100))), dict(seq_id=1, tokens=seqs[1][:1], want=[0])])
+    got[0].append(out[:100]); got[1].append(out[100:])
+    fed = [100, 1]
+    while fed[0] < 300 or fed[1] < 270:
+        live = [i for i in (0, 1) if fed[i] < len(seqs[i])]
+        out = runner.execute([dict(seq_id=i, tokens=[seqs[i][fed[i]]], want=[0]) for i in live])
+        for r, i in enumerate(live):
+            got[i].append(out[r:r + 1]); fed[i] += 1
+    for i in (0, 1):
+        close(torch.cat(got[i]), refs[i], TOL[torch.bfloat16], f"{name} request {i}")
 
 
 @pytest.mark.parametrize("name", ["loop2", "plain"])
