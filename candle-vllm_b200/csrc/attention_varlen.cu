@@ -25,6 +25,8 @@ qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float
                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int32_t* __restrict__ positions,
                           const int64_t* __restrict__ slot_mapping, TQ* __restrict__ q_out, TC* __restrict__ k_cache,
                           TC* __restrict__ v_cache, int H, int G, int dk, int dv, int rot_dims, float eps) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float red[2][8];
     const int t = blockIdx.x;
     const float* row = qkv + (int64_t)t * ld;
@@ -73,6 +75,8 @@ qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float
 __global__ void chunk_decode_view_kernel(const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ positions,
                                          uint32_t* __restrict__ out_tables, uint32_t* __restrict__ out_ctx, int num_seqs, int out_width,
                                          int block_size, int chunk) {
+    pdl_wait();
+    pdl_trigger();
     const int b = blockIdx.x;
     const int pos = positions[b];
     const int cs = (pos / chunk) * chunk;
@@ -90,6 +94,8 @@ paged_attention_varlen_kernel(const TQ* __restrict__ q, const TC* __restrict__ k
                               const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ token_seq,
                               const int32_t* __restrict__ positions, TOut* __restrict__ out, int64_t items, int H, int G, int dk, int dv,
                               int block_size, float scale, int chunk, int window) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ float qsm[];                  // [4 warps][dk]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t item = (int64_t)blockIdx.x * 4 + warp;
@@ -167,8 +173,8 @@ void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, con
                  ld >= (int64_t)num_heads * dk + (int64_t)num_kv_heads * (dk + dv) && (!cos_t || max_pos > 0),
                  kErrBadArg, "qk_norm_rope_cache: bad sizes");
     cudaStream_t st = as_stream(stream);
-#define QNRC(TC, TQ) qk_norm_rope_cache_kernel<TC, TQ><<<num_tokens, 256, 0, st>>>(qkv, ld, q_norm_w, k_norm_w, cos_t, sin_t, positions, slot_mapping, \
-        (TQ*)q_out, (TC*)key_cache, (TC*)value_cache, num_heads, num_kv_heads, dk, dv, rot_dims, eps)
+#define QNRC(TC, TQ) launch_pdl(qk_norm_rope_cache_kernel<TC, TQ>, dim3(num_tokens), dim3(256), 0, st, qkv, ld, q_norm_w, k_norm_w, cos_t, sin_t, positions, \
+        slot_mapping, (TQ*)q_out, (TC*)key_cache, (TC*)value_cache, num_heads, num_kv_heads, dk, dv, rot_dims, eps)
     if (cache_dtype == B200_F32 && q_dtype == B200_F32) QNRC(float, float);
     else if (cache_dtype == B200_BF16 && q_dtype == B200_F32) QNRC(__nv_bfloat16, float);
     else if (cache_dtype == B200_BF16 && q_dtype == B200_BF16) QNRC(__nv_bfloat16, __nv_bfloat16);
@@ -183,8 +189,8 @@ void chunk_decode_view(const int32_t* block_tables, int32_t table_width, const i
     if (num_seqs == 0) return;
     B200_REQUIRE(block_tables && positions && out_tables && out_ctx && table_width > 0 && out_width > 0 && block_size > 0 && chunk > 0 &&
                  chunk % block_size == 0, kErrBadArg, "chunk_decode_view: bad arguments (chunk must be a multiple of the block size)");
-    chunk_decode_view_kernel<<<num_seqs, 64, 0, as_stream(stream)>>>(block_tables, table_width, positions, out_tables, out_ctx, num_seqs, out_width,
-                                                                     block_size, chunk);
+    launch_pdl(chunk_decode_view_kernel, dim3(num_seqs), dim3(64), 0, as_stream(stream), block_tables, table_width, positions, out_tables, out_ctx, num_seqs,
+               out_width, block_size, chunk);
     count_launch();
     check_launch("chunk_decode_view");
 }
@@ -214,8 +220,8 @@ void paged_attention_varlen(void* out, const void* q, const void* key_cache, con
     const int64_t items = (int64_t)num_tokens * num_heads;
     const unsigned grid = (unsigned)((items + 3) / 4);
     const size_t smem = (size_t)4 * dk * sizeof(float);
-#define PAV(TC, TO, TQ) paged_attention_varlen_kernel<TC, TO, TQ><<<grid, 128, smem, st>>>((const TQ*)q, (const TC*)key_cache, (const TC*)value_cache, block_tables, \
-        table_width, token_seq, positions, (TO*)out, items, num_heads, num_kv_heads, dk, dv, block_size, scale, chunk, window)
+#define PAV(TC, TO, TQ) launch_pdl(paged_attention_varlen_kernel<TC, TO, TQ>, dim3(grid), dim3(128), smem, st, (const TQ*)q, (const TC*)key_cache, \
+        (const TC*)value_cache, block_tables, table_width, token_seq, positions, (TO*)out, items, num_heads, num_kv_heads, dk, dv, block_size, scale, chunk, window)
     if (cache_dtype == B200_F32 && out_dtype == B200_F32 && q_dtype == B200_F32) PAV(float, float, float);
     else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16 && q_dtype == B200_F32) PAV(__nv_bfloat16, __nv_bfloat16, float);
     else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16 && q_dtype == B200_BF16) PAV(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);

@@ -28,6 +28,8 @@ __global__ void __launch_bounds__(128)
 causal_conv_silu_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ taps, const float* __restrict__ conv_state,
                         float* __restrict__ y, const int32_t* __restrict__ token_seq, const int32_t* __restrict__ cu_seqlens,
                         const int32_t* __restrict__ seq_slots, const int32_t* __restrict__ seq_start, int C, int K) {
+    pdl_wait();
+    pdl_trigger();
     const int c = blockIdx.x * 128 + threadIdx.x;
     const int t = blockIdx.y;
     if (c >= C) return;
@@ -49,6 +51,8 @@ causal_conv_silu_kernel(const float* __restrict__ x, int64_t ldx, const float* _
 __global__ void __launch_bounds__(128)
 causal_conv_update_kernel(const float* __restrict__ x, int64_t ldx, float* __restrict__ conv_state, const int32_t* __restrict__ cu_seqlens,
                           const int32_t* __restrict__ seq_slots, const int32_t* __restrict__ seq_start, int C, int K) {
+    pdl_wait();
+    pdl_trigger();
     const int c = blockIdx.x * 128 + threadIdx.x;
     const int b = blockIdx.y;
     if (c >= C) return;
@@ -82,6 +86,8 @@ gated_delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__
                         const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ state, float* __restrict__ out,
                         const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ seq_slots, const int32_t* __restrict__ seq_start,
                         int H, int G, int dk, int dv) {
+    pdl_wait();
+    pdl_trigger();
     constexpr int kDP = 4 * kR;                       // padded key size
     constexpr int kNQ = kTile * kDP / 128;            // q (and k) elements a thread stages per tile
     extern __shared__ float sm[];
@@ -201,6 +207,8 @@ template <typename TOut>
 __global__ void __launch_bounds__(128)
 gated_rms_norm_kernel(const float* __restrict__ o, const float* __restrict__ gate, int64_t ld_gate, const float* __restrict__ w,
                       TOut* __restrict__ out, int64_t items, int H, int dv, float eps) {
+    pdl_wait();
+    pdl_trigger();
     const int64_t item = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (item >= items) return;
@@ -229,12 +237,12 @@ void causal_conv_silu(const float* x, int64_t ldx, const float* taps, float* con
     B200_REQUIRE(x && taps && conv_state && y && token_seq && cu_seqlens && seq_slots && seq_start && channels > 0 && num_taps >= 1 &&
                  ldx >= channels, kErrBadArg, "causal_conv_silu: bad arguments");
     cudaStream_t st = as_stream(stream);
-    causal_conv_silu_kernel<<<dim3(ceil_div(channels, 128), num_tokens), 128, 0, st>>>(x, ldx, taps, conv_state, y, token_seq, cu_seqlens,
-                                                                                         seq_slots, seq_start, channels, num_taps);
+    launch_pdl(causal_conv_silu_kernel, dim3(ceil_div(channels, 128), num_tokens), dim3(128), 0, st, x, ldx, taps, (const float*)conv_state, y, token_seq,
+               cu_seqlens, seq_slots, seq_start, channels, num_taps);
     count_launch();
     if (num_taps > 1) {
-        causal_conv_update_kernel<<<dim3(ceil_div(channels, 128), num_seqs), 128, 0, st>>>(x, ldx, conv_state, cu_seqlens, seq_slots, seq_start,
-                                                                                            channels, num_taps);
+        launch_pdl(causal_conv_update_kernel, dim3(ceil_div(channels, 128), num_seqs), dim3(128), 0, st, x, ldx, conv_state, cu_seqlens, seq_slots, seq_start,
+                   channels, num_taps);
         count_launch();
     }
     check_launch("causal_conv_silu");
@@ -253,8 +261,8 @@ void gated_delta_rule(const float* qkv, const float* proj, int64_t ld_proj, int3
 #define GDR(R) do { \
         const int smem = (2 * kTile * 4 * R + kTile * 32 + 2 * kTile) * (int)sizeof(float); \
         ensure_dynamic_smem(reinterpret_cast<const void*>(gated_delta_rule_kernel<R>), smem); \
-        gated_delta_rule_kernel<R><<<grid, 128, smem, st>>>(qkv, proj, ld_proj, off_b, off_a, A_log, dt_bias, state, out, cu_seqlens, seq_slots, \
-                                                            seq_start, num_heads, num_kv_heads, dk, dv); } while (0)
+        launch_pdl(gated_delta_rule_kernel<R>, grid, dim3(128), smem, st, qkv, proj, ld_proj, off_b, off_a, A_log, dt_bias, state, out, cu_seqlens, seq_slots, \
+                   seq_start, num_heads, num_kv_heads, dk, dv); } while (0)
     if (dk <= 32) GDR(8);
     else if (dk <= 64) GDR(16);
     else if (dk <= 128) GDR(32);
@@ -271,8 +279,8 @@ void gated_rms_norm(const float* o, const float* gate, int64_t ld_gate, const fl
     const int64_t items = (int64_t)num_tokens * num_heads;
     const unsigned grid = (unsigned)((items + 3) / 4);
     cudaStream_t st = as_stream(stream);
-    if (out_dtype == B200_F32) gated_rms_norm_kernel<float><<<grid, 128, 0, st>>>(o, gate, ld_gate, weight, (float*)out, items, num_heads, dv, eps);
-    else if (out_dtype == B200_BF16) gated_rms_norm_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(o, gate, ld_gate, weight, (__nv_bfloat16*)out, items, num_heads, dv, eps);
+    if (out_dtype == B200_F32) launch_pdl(gated_rms_norm_kernel<float>, dim3(grid), dim3(128), 0, st, o, gate, ld_gate, weight, (float*)out, items, num_heads, dv, eps);
+    else if (out_dtype == B200_BF16) launch_pdl(gated_rms_norm_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, o, gate, ld_gate, weight, (__nv_bfloat16*)out, items, num_heads, dv, eps);
     else { set_error(kErrUnsupported, "gated_rms_norm: out dtype %d (f32 / bf16)", out_dtype); return; }
     count_launch();
     check_launch("gated_rms_norm");

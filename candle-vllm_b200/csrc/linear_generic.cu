@@ -19,6 +19,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 linear_generic_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restrict__ y, int m, int n, int k, int64_t ldx,
                       int64_t ldw, int64_t ldy) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float xs[kTK][kTM + 4], ws[kTK][kTN + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int row0 = blockIdx.y * kTM, col0 = blockIdx.x * kTN;
@@ -66,6 +68,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 linear_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restrict__ y, int m, int n, int k, int64_t ldx, int64_t ldw,
                    int64_t ldy) {
+    pdl_wait();
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col = blockIdx.x * 8 + warp;
     const int r0 = blockIdx.y * 4;
@@ -88,9 +92,9 @@ linear_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __re
 template <typename T>
 void launch_generic(const void* x, const void* w, float* y, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldy, cudaStream_t st) {
     if (m <= 8)
-        linear_rows_kernel<T><<<dim3(ceil_div(n, 8), ceil_div(m, 4)), 256, 0, st>>>((const T*)x, (const T*)w, y, m, n, k, ldx, ldw, ldy);
+        launch_pdl(linear_rows_kernel<T>, dim3(ceil_div(n, 8), ceil_div(m, 4)), dim3(256), 0, st, (const T*)x, (const T*)w, y, m, n, k, ldx, ldw, ldy);
     else
-        linear_generic_kernel<T><<<dim3(ceil_div(n, kTN), ceil_div(m, kTM)), 256, 0, st>>>((const T*)x, (const T*)w, y, m, n, k, ldx, ldw, ldy);
+        launch_pdl(linear_generic_kernel<T>, dim3(ceil_div(n, kTN), ceil_div(m, kTM)), dim3(256), 0, st, (const T*)x, (const T*)w, y, m, n, k, ldx, ldw, ldy);
     count_launch();
 }
 

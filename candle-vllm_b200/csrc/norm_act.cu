@@ -26,6 +26,8 @@ template <typename TOut>
 __global__ void __launch_bounds__(256)
 rms_norm_ex_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* out, const float* residual,
                    const int32_t* __restrict__ row_index, int n, int64_t ldx, float eps, float offset) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float red[8];
     const int row = blockIdx.x;
     const int64_t src = row_index ? row_index[row] : row;
@@ -48,6 +50,8 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 
 template <typename TOut>
 __global__ void gelu_tanh_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int64_t rows, int ff, int64_t ld) {
+    pdl_wait();
+    pdl_trigger();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= rows * ff) return;
     const int64_t r = i / ff;
@@ -59,6 +63,8 @@ __global__ void gelu_tanh_mul_kernel(const float* __restrict__ gu, TOut* __restr
 template <typename TTab>
 __global__ void embedding_scaled_kernel(const TTab* __restrict__ table, const int32_t* __restrict__ ids, float* __restrict__ out, int dim,
                                         int vocab, float scale) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -78,8 +84,8 @@ void rms_norm_ex(const float* x, const float* weight, void* out, const float* re
     B200_REQUIRE(x && weight && out && rows > 0 && n > 0 && ldx >= n, kErrBadArg, "rms_norm_ex: bad arguments");
     B200_REQUIRE(!residual || out_dtype == B200_F32, kErrUnsupported, "rms_norm_ex: the residual sum is f32");
     cudaStream_t st = as_stream(stream);
-    if (out_dtype == B200_F32) rms_norm_ex_kernel<float><<<rows, 256, 0, st>>>(x, weight, (float*)out, residual, row_index, n, ldx, eps, weight_offset);
-    else if (out_dtype == B200_BF16) rms_norm_ex_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(x, weight, (__nv_bfloat16*)out, residual, row_index, n, ldx, eps, weight_offset);
+    if (out_dtype == B200_F32) launch_pdl(rms_norm_ex_kernel<float>, dim3(rows), dim3(256), 0, st, x, weight, (float*)out, residual, row_index, n, ldx, eps, weight_offset);
+    else if (out_dtype == B200_BF16) launch_pdl(rms_norm_ex_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, st, x, weight, (__nv_bfloat16*)out, residual, row_index, n, ldx, eps, weight_offset);
     else { set_error(kErrUnsupported, "rms_norm_ex: out dtype %d (f32 / bf16)", out_dtype); return; }
     count_launch();
     check_launch("rms_norm_ex");
@@ -91,8 +97,8 @@ void gelu_tanh_mul(const float* gate_up, void* out, int64_t rows, int32_t ff, in
     const int64_t total = rows * ff;
     const unsigned grid = (unsigned)((total + 255) / 256);
     cudaStream_t st = as_stream(stream);
-    if (out_dtype == B200_F32) gelu_tanh_mul_kernel<float><<<grid, 256, 0, st>>>(gate_up, (float*)out, rows, ff, ld);
-    else if (out_dtype == B200_BF16) gelu_tanh_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(gate_up, (__nv_bfloat16*)out, rows, ff, ld);
+    if (out_dtype == B200_F32) launch_pdl(gelu_tanh_mul_kernel<float>, dim3(grid), dim3(256), 0, st, gate_up, (float*)out, rows, ff, ld);
+    else if (out_dtype == B200_BF16) launch_pdl(gelu_tanh_mul_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, gate_up, (__nv_bfloat16*)out, rows, ff, ld);
     else { set_error(kErrUnsupported, "gelu_tanh_mul: out dtype %d (f32 / bf16)", out_dtype); return; }
     count_launch();
     check_launch("gelu_tanh_mul");
@@ -103,8 +109,8 @@ void embedding_scaled(const void* table, const int32_t* ids, float* out, int32_t
     if (num_tokens == 0) return;
     B200_REQUIRE(table && ids && out && dim > 0 && vocab > 0, kErrBadArg, "embedding_scaled: bad arguments");
     cudaStream_t st = as_stream(stream);
-    if (table_dtype == B200_F32) embedding_scaled_kernel<float><<<num_tokens, 128, 0, st>>>((const float*)table, ids, out, dim, vocab, scale);
-    else if (table_dtype == B200_BF16) embedding_scaled_kernel<__nv_bfloat16><<<num_tokens, 128, 0, st>>>((const __nv_bfloat16*)table, ids, out, dim, vocab, scale);
+    if (table_dtype == B200_F32) launch_pdl(embedding_scaled_kernel<float>, dim3(num_tokens), dim3(128), 0, st, (const float*)table, ids, out, dim, vocab, scale);
+    else if (table_dtype == B200_BF16) launch_pdl(embedding_scaled_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, st, (const __nv_bfloat16*)table, ids, out, dim, vocab, scale);
     else { set_error(kErrUnsupported, "embedding_scaled: table dtype %d (f32 / bf16)", table_dtype); return; }
     count_launch();
     check_launch("embedding_scaled");
