@@ -787,7 +787,9 @@ def run_gobesun(args):
         def work(tag, key, T):
             if key.startswith("linear["):
                 n, k = (int(v) for v in key[7:-1].split("x"))
-                return ("flops", 2.0 * T * n * k) if tag == "prefill" else ("bytes", n * k * esz + T * (k * esz + n * 4))
+                if n == V and tag == "prefill":
+                    T = 1                           # only the last row of a prompt goes through the head
+                return ("flops", 2.0 * T * n * k) if (tag == "prefill" and T > 1) else ("bytes", n * k * esz + T * (k * esz + n * 4))
             return {
                 "rms_norm_ex": ("bytes", T * D * (4 + esz)), "rms_norm": ("bytes", T * D * (4 + esz)),
                 "gelu_tanh_mul": ("bytes", T * ff * (8 + esz)), "silu_mul": ("bytes", T * ff * (8 + esz)),

@@ -112,7 +112,23 @@ void linear_f32out(const void* x, const void* weight, float* out, int32_t m, int
     cudaStream_t st = as_stream(stream);
     if (dtype == B200_BF16) {
         const bool tma_ok = k % 8 == 0 && ldx % 8 == 0 && ((((uintptr_t)x) | ((uintptr_t)weight)) & 15) == 0 && k >= 64;
-        if (tma_ok) { dense_gemm_16(x, weight, nullptr, out, m, n, k, ldx, k, ldy, B200_BF16, B200_F32, st, 0, 0); return; }
+        if (tma_ok) {
+            // few rows = a pure weight stream: with fewer 128-row weight tiles than SMs the kernel cuts k so that every SM streams a part and
+            // the parts meet in fp32 atomics on a zeroed output (the condition mirrors dense_gemm_16's own)
+            int split = 0;
+            if (m <= 64) {
+                const int tiles = (n + 127) / 128, nkb = (k + 63) / 64;
+                int ks = tiles < sm_count() ? sm_count() / tiles : 1;
+                if (ks > nkb / 4) ks = nkb / 4;
+                split = ks > 1 ? 1 : 0;
+            }
+            if (split) {
+                if (ldy == n) cudaMemsetAsync(out, 0, (size_t)m * n * sizeof(float), st);
+                else cudaMemset2DAsync(out, (size_t)ldy * sizeof(float), 0, (size_t)n * sizeof(float), (size_t)m, st);
+            }
+            dense_gemm_16(x, weight, nullptr, out, m, n, k, ldx, k, ldy, B200_BF16, B200_F32, st, 0, split);
+            return;
+        }
         launch_generic<__nv_bfloat16>(x, weight, out, m, n, k, ldx, k, ldy, st);
     } else if (dtype == B200_F32) {
         launch_generic<float>(x, weight, out, m, n, k, ldx, k, ldy, st);
