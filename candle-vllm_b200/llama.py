@@ -194,3 +194,46 @@ class GGUFLLaMa:
 
     def kernel_launches(self) -> int:
         return int(lib().b200_llama_kernel_launches(self._h))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# dense safetensors checkpoints (the reference's llama.rs path): config.json + model.safetensors -> the dict GGUFLLaMa takes
+# ---------------------------------------------------------------------------------------------------------------------
+class LlamaCheckpoint:
+    """What ``registry.load_model`` returns for ``LlamaForCausalLM``: the configuration and the weights in the engine's layout.  The Llama
+    engine is decode-only and owns its step (C++ graph replay), so unlike the ragged-step models it is not driven by ``ModelRunner``;
+    ``make_engine(kv_cache)`` builds the ``GGUFLLaMa`` over a ``CacheEngine``'s tensors."""
+    architecture = "LlamaForCausalLM"
+
+    def __init__(self, cfg: LlamaConfig, weights: dict):
+        self.cfg, self.weights = cfg, weights
+
+    def make_engine(self, kv_cache: List, **kw) -> "GGUFLLaMa":
+        return GGUFLLaMa(self.cfg, self.weights, kv_cache, rope_neox=True, **kw)
+
+
+def load_dense_checkpoint(path: str, dtype: torch.dtype = torch.bfloat16, device="cuda", block_size: int = 64, max_num_seqs: int = 32,
+                          max_blocks_per_seq: int = 128, **_) -> LlamaCheckpoint:
+    import json
+    import os
+    from .safetensors_io import load_file
+    with open(os.path.join(path, "config.json")) as f:
+        c = json.load(f)
+    heads = int(c["num_attention_heads"])
+    cfg = LlamaConfig(hidden=int(c["hidden_size"]), num_layers=int(c["num_hidden_layers"]), num_heads=heads,
+                      num_kv_heads=int(c.get("num_key_value_heads", heads)), head_dim=int(c.get("head_dim") or int(c["hidden_size"]) // heads),
+                      ffn=int(c["intermediate_size"]), vocab=int(c["vocab_size"]), rms_eps=float(c.get("rms_norm_eps", 1e-5)),
+                      rope_theta=float(c.get("rope_theta", 10000.0)), max_pos=int(c.get("max_position_embeddings", 8192)), block_size=block_size,
+                      max_num_seqs=max_num_seqs, max_blocks_per_seq=max_blocks_per_seq)
+    t = load_file(os.path.join(path, "model.safetensors"))
+    f32 = lambda n: t[n].float().to(device).contiguous()
+    w16 = lambda n: t[n].to(dtype).to(device).contiguous()
+    w = dict(tok_embeddings=f32("model.embed_tokens.weight"), norm=f32("model.norm.weight"),
+             output=w16("lm_head.weight" if "lm_head.weight" in t else "model.embed_tokens.weight"), layers=[])
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}."
+        w["layers"].append(dict(attn_norm=f32(p + "input_layernorm.weight"), ffn_norm=f32(p + "post_attention_layernorm.weight"),
+                                wq=w16(p + "self_attn.q_proj.weight"), wk=w16(p + "self_attn.k_proj.weight"), wv=w16(p + "self_attn.v_proj.weight"),
+                                wo=w16(p + "self_attn.o_proj.weight"), w1=w16(p + "mlp.gate_proj.weight"), w2=w16(p + "mlp.down_proj.weight"),
+                                w3=w16(p + "mlp.up_proj.weight")))
+    return LlamaCheckpoint(cfg, w)

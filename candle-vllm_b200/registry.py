@@ -42,4 +42,10 @@ def _gobesun(path, **kw):
     return GobesunModel.from_pretrained(path, **kw)
 
 
+def _llama(path, **kw):
+    from .llama import load_dense_checkpoint
+    return load_dense_checkpoint(path, **kw)
+
+
 register_model("Gobesun", _gobesun)
+register_model("LlamaForCausalLM", _llama)

@@ -293,6 +293,10 @@ CONFIGS["wide"] = S.gobesun_config(64, 80, [S.gobesun_attention_layer(2, 1, 128,
 # the same with chunks that start on block borders: single-token steps in bf16 then run on the split-KV decode kernel
 CONFIGS["wide64"] = S.gobesun_config(64, 80, [S.gobesun_delta_layer(2, 2, 64, 16, conv=3), S.gobesun_attention_layer(4, 2, 128, 128, 128, 32, ff=96)],
                                      loop=dict(start=1, stop=2, times=2))
+# degenerate sizes: a 1-tap convolution (no carried inputs), rotation of the whole head without scaling, one pass of a one-layer loop,
+# odd width / vocabulary / ff (no 8-element alignment anywhere), only recurrent + one attention layer without feed-forward
+CONFIGS["odd"] = S.gobesun_config(52, 61, [S.gobesun_delta_layer(2, 1, 20, 12, conv=1, ff=44), S.gobesun_attention_layer(3, 3, 12, 20, 50, 12)],
+                                  loop=dict(start=1, stop=2, times=1), eps=1e-5, embedding_scale=3.0)
 CONFIGS["plain"].pop("loop")
 _CACHE = {}
 

@@ -121,6 +121,25 @@ def test_registry_picks_the_class_by_config(tmp_path):
         load_model(str(tmp_path))
 
 
+def test_registry_loads_a_dense_llama_checkpoint(tmp_path):
+    """the other family goes through the same door: HF-style names -> the layout the decode engine takes"""
+    D, ff, V, H, G, hd = 32, 48, 40, 2, 1, 16
+    t = {"model.embed_tokens.weight": torch.randn(V, D), "model.norm.weight": torch.ones(D), "lm_head.weight": torch.randn(V, D)}
+    p = "model.layers.0."
+    t.update({p + "input_layernorm.weight": torch.ones(D), p + "post_attention_layernorm.weight": torch.ones(D),
+              p + "self_attn.q_proj.weight": torch.randn(H * hd, D), p + "self_attn.k_proj.weight": torch.randn(G * hd, D),
+              p + "self_attn.v_proj.weight": torch.randn(G * hd, D), p + "self_attn.o_proj.weight": torch.randn(D, H * hd),
+              p + "mlp.gate_proj.weight": torch.randn(ff, D), p + "mlp.up_proj.weight": torch.randn(ff, D), p + "mlp.down_proj.weight": torch.randn(D, ff)})
+    save_file({k: v.to(torch.bfloat16) for k, v in t.items()}, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(dict(architectures=["LlamaForCausalLM"], hidden_size=D, num_hidden_layers=1, num_attention_heads=H,
+                                                          num_key_value_heads=G, intermediate_size=ff, vocab_size=V, rms_norm_eps=1e-6, rope_theta=5e5)))
+    ck = load_model(str(tmp_path), device="cpu")
+    assert ck.cfg.head_dim == hd and ck.cfg.num_kv_heads == G and ck.cfg.ffn == ff and ck.cfg.rope_theta == 5e5
+    L = ck.weights["layers"][0]
+    assert L["w1"].shape == (ff, D) and L["w2"].shape == (D, ff) and L["wq"].dtype == torch.bfloat16 and ck.weights["tok_embeddings"].dtype == torch.float32
+    assert torch.equal(L["w3"], t[p + "mlp.up_proj.weight"].to(torch.bfloat16))
+
+
 def test_config_layer_runs_and_validation():
     L = [S.gobesun_delta_layer(2, 1, 32, 16), S.gobesun_attention_layer(2, 2, 16, 16, 32, 8), S.gobesun_delta_layer(2, 2, 32, 16)]
     assert GobesunConfig.from_dict(S.gobesun_config(32, 40, L, loop=dict(start=1, stop=3, times=2))).layer_runs() == [0, 1, 2, 1, 2]
