@@ -503,3 +503,38 @@ def test_graph_replay_of_decode_steps_matches_eager():
     assert 1 in runner._graphs            # (the two-entry graph was dropped when the rotary tables grew, and captured again while needed)
     for i in (0, 1):
         close(torch.cat(got[i]), refs[i], TOL[torch.float32], f"graph replay, request {i}")
+
+
+def test_command_line_and_trace_runner(tmp_path):
+    """the two programs a user starts, as child processes on a checkpoint on disk: `generate` against the oracle's greedy continuation,
+    `bin/trace_run` fed two steps (a portion of one request beside the first token of another, then single tokens; the first request ends)
+    against the oracle's logits"""
+    import json, os, subprocess, sys
+    from candle_vllm_b200.safetensors_io import save_file
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = CONFIGS["plain"]
+    w = S.gobesun_weights(cfg, 7)
+    save_file(w, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    prompt = [5, 9, 2, 44, 17, 3]
+    r = subprocess.run([sys.executable, "-m", "candle_vllm_b200", "generate", "--model", str(tmp_path), "--dtype", "float32", "--prompt-ids",
+                        ",".join(map(str, prompt)), "--max-new-tokens", "5"], capture_output=True, text=True, env=env, cwd=root, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["output"] == G.greedy(cfg, w, prompt, 5)
+
+    a, b = list(range(1, 71)), [7, 8, 9]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:69], "want": [0, 68]}, {"id": "b", "tokens": b[:1], "want": [0]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[69:], "want": [0]}, {"id": "b", "tokens": b[1:2], "want": []}], "end": ["a"]},
+             {"step": 2, "entries": [{"id": "b", "tokens": b[2:], "want": [0]}, {"id": "c", "tokens": a[:2], "want": [1]}], "end": ["b", "c"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out), "--max-tokens", "192"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, env=env, cwd=root, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    ra, rb = G.forward(cfg, w, a), G.forward(cfg, w, b)
+    V = cfg["vocab"]
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", np.float32).reshape(-1, V))
+    close(got0, torch.stack([ra[0], ra[68], rb[0]]), TOL[torch.float32], "step 0")
+    close(torch.from_numpy(np.fromfile(out / "1.f32", np.float32).reshape(-1, V)), ra[69:70], TOL[torch.float32], "step 1")
+    close(torch.from_numpy(np.fromfile(out / "2.f32", np.float32).reshape(-1, V)), torch.stack([rb[2], ra[1]]), TOL[torch.float32], "step 2")
