@@ -11,7 +11,7 @@
 //                           what that kernel reads).
 //   gated_delta_rule        per head, S [dk, dv]:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                           with q, k made unit vectors (q also times dk^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) *
-//                           softplus(a + dt_bias)).  A block owns 32 value columns of one head of one entry with its slice of S in
+//                           softplus(a + dt_bias)).  A block owns 16 value columns of one head of one entry with its slice of S in
 //                           registers and walks the portion in tiles of 16 tokens staged through shared memory, the next
 //                           tile in flight while the current one is applied.  Decode (one token per entry) is one read and
 //                           one write of the state.
@@ -71,12 +71,15 @@ causal_conv_update_kernel(const float* __restrict__ x, int64_t ldx, float* __res
     }
 }
 
-// A block of four warps owns 32 value columns of one head of one entry (8 per warp); inside a warp the key rows are split four ways
-// (lane = 8 * part + column, part p holds rows p * kR .. p * kR + kR - 1 of its column in registers), so a token costs kR multiply-adds
-// per lane per pass instead of dk and two butterfly steps join the four partial sums.  kR = rows per part (dk <= 4 * kR; rows past dk are
-// zero and stay zero).  Tokens are taken in tiles of 16: the block loads the NEXT tile's q, k, v, a, b into registers (coalesced, all in
-// flight at once) while it walks the current tile out of shared memory, where q and k were made unit vectors and beta / decay were
-// worked out for all 16 tokens in parallel -- the serial part of a token is then two short multiply-add chains and two butterflies.
+// A block of four warps owns 16 value columns of one head of one entry (4 per warp); inside a warp the key rows are split eight ways
+// (lane = 4 * part + column, part p holds rows p * kR .. p * kR + kR - 1 of its column in registers), so a token costs kR multiply-adds
+// per lane per pass instead of dk and three butterfly steps join the eight partial sums.  kR = rows per part (dk <= 8 * kR; rows past dk
+// are zero and stay zero).  The state is stored [slot, head, column, row]: a lane's rows are contiguous (16-byte loads and stores).
+// Tokens are taken in tiles of 16: the block loads the NEXT tile's q, k, v, a, b into registers (coalesced, all in flight at once) while
+// it walks the current tile out of shared memory, where q and k were made unit vectors and beta, decay and k . q were worked out for all
+// 16 tokens in parallel.  Both read-outs of a token are taken from the state as the previous token left it (S0^T k and S0^T q; the
+// current token's write enters the output as u (k . q)), so the serial part of a token is one pass of multiply-adds, one butterfly
+// round that joins both sums, and the update pass.
 // Every sum has a fixed order, so portions of any size give the same state bit for bit.
 constexpr int kTile = 16;
 
@@ -88,33 +91,43 @@ gated_delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__
                         int H, int G, int dk, int dv) {
     pdl_wait();
     pdl_trigger();
-    constexpr int kDP = 4 * kR;                       // padded key size
+    constexpr int kDP = 8 * kR;                       // padded key size
     constexpr int kNQ = kTile * kDP / 128;            // q (and k) elements a thread stages per tile
     extern __shared__ float sm[];
     float* qs = sm;                                   // [kTile][kDP]
     float* ks = qs + kTile * kDP;                     // [kTile][kDP]
-    float* vs = ks + kTile * kDP;                     // [kTile][32]
-    float* bs = vs + kTile * 32;                      // [kTile] b, then beta
+    float* vs = ks + kTile * kDP;                     // [kTile][16]
+    float* bs = vs + kTile * 16;                      // [kTile] b, then beta
     float* ds = bs + kTile;                           // [kTile] a, then decay
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, part = lane >> 3;
+    float* kqs = ds + kTile;                          // [kTile] k . q of the unit vectors
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, part = lane >> 2;
     const int b = blockIdx.z, h = blockIdx.y;
-    const int col = blockIdx.x * 32 + warp * 8 + (lane & 7);
+    const int col = blockIdx.x * 16 + warp * 4 + (lane & 3);
     const bool live = col < dv;
     const int g = h / (H / G);
     const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
     if (n <= 0) return;
     const int C = 2 * G * dk + H * dv;
     const int row0 = part * kR;
-    float* Sg = state + (((int64_t)seq_slots[b] * H + h) * dk + row0) * dv + col;
+    float* Sg = state + (((int64_t)seq_slots[b] * H + h) * dv + (live ? col : 0)) * dk + row0;
     const bool fresh = seq_start[b] == 0;
+    const bool vec = (dk & 3) == 0 && row0 + kR <= dk;           // this lane's rows: whole float4s inside the key size
     float S[kR];
+    if (live && !fresh && vec) {
 #pragma unroll
-    for (int r = 0; r < kR; ++r) S[r] = (live && !fresh && row0 + r < dk) ? Sg[(int64_t)r * dv] : 0.f;
+        for (int r = 0; r < kR; r += 4) {
+            const float4 t4 = *reinterpret_cast<const float4*>(Sg + r);
+            S[r] = t4.x; S[r + 1] = t4.y; S[r + 2] = t4.z; S[r + 3] = t4.w;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < kR; ++r) S[r] = (live && !fresh && row0 + r < dk) ? Sg[r] : 0.f;
+    }
     const float neg_rate = -expf(A_log[h]);
     const float bias = dt_bias[h];
     const float qscale = 1.0f / sqrtf((float)dk);
 
-    float rq[kNQ], rk[kNQ], rv[kTile * 32 / 128], ra = 0.f, rb = 0.f;
+    float rq[kNQ], rk[kNQ], rv[kTile * 16 / 128], ra = 0.f, rb = 0.f;
     auto load_tile = [&](int first, int cnt) {        // global -> registers
 #pragma unroll
         for (int j = 0; j < kNQ; ++j) {
@@ -125,8 +138,8 @@ gated_delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__
             rk[j] = in ? row[G * dk] : 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < kTile * 32 / 128; ++j) {
-            const int e = tid + 128 * j, tt = e >> 5, c = blockIdx.x * 32 + (e & 31);
+        for (int j = 0; j < kTile * 16 / 128; ++j) {
+            const int e = tid + 128 * j, tt = e >> 4, c = blockIdx.x * 16 + (e & 15);
             rv[j] = (tt < cnt && c < dv) ? qkv[(int64_t)(first + tt) * C + 2 * G * dk + h * dv + c] : 0.f;
         }
         if (tid < kTile && tid < cnt) {
@@ -138,26 +151,32 @@ gated_delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__
 #pragma unroll
         for (int j = 0; j < kNQ; ++j) { qs[tid + 128 * j] = rq[j]; ks[tid + 128 * j] = rk[j]; }
 #pragma unroll
-        for (int j = 0; j < kTile * 32 / 128; ++j) vs[tid + 128 * j] = rv[j];
+        for (int j = 0; j < kTile * 16 / 128; ++j) vs[tid + 128 * j] = rv[j];
         if (tid < kTile) { bs[tid] = rb; ds[tid] = ra; }
     };
     auto prepare_tile = [&](int cnt) {                 // unit vectors, beta, decay: 4 tokens per warp, in parallel
         for (int tt = warp; tt < cnt; tt += 4) {
-            float qq = 0.f, kk = 0.f;
-            for (int i = lane; i < kDP; i += 32) { const float a = qs[tt * kDP + i], c = ks[tt * kDP + i]; qq = fmaf(a, a, qq); kk = fmaf(c, c, kk); }
-            qq = warp_sum(qq); kk = warp_sum(kk);
+            float qq = 0.f, kk = 0.f, qk = 0.f;
+            for (int i = lane; i < kDP; i += 32) {
+                const float a = qs[tt * kDP + i], c = ks[tt * kDP + i];
+                qq = fmaf(a, a, qq); kk = fmaf(c, c, kk); qk = fmaf(a, c, qk);
+            }
+            qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
             const float qn = qscale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
             for (int i = lane; i < kDP; i += 32) { qs[tt * kDP + i] *= qn; ks[tt * kDP + i] *= kn; }
             if (lane == 0) {
+                kqs[tt] = qk * qn * kn;
                 bs[tt] = 1.0f / (1.0f + expf(-bs[tt]));
                 ds[tt] = expf(neg_rate * softplus_f(ds[tt] + bias));
             }
         }
     };
-    auto join4 = [](float v) {                         // sum over the four parts (lanes that differ in bits 3 and 4)
-        v += __shfl_xor_sync(0xffffffffu, v, 8);
-        v += __shfl_xor_sync(0xffffffffu, v, 16);
-        return v;
+    auto join8 = [](float& a, float& c) {              // sums over the eight parts (lanes that differ in bits 2, 3 and 4), two at a time
+#pragma unroll
+        for (int m = 4; m <= 16; m <<= 1) {
+            const float x = __shfl_xor_sync(0xffffffffu, a, m), y = __shfl_xor_sync(0xffffffffu, c, m);
+            a += x; c += y;
+        }
     };
 
     const int tiles = (n + kTile - 1) / kTile;
@@ -173,33 +192,37 @@ gated_delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__
         for (int tt = 0; tt < cnt; ++tt) {
             const float4* k4 = reinterpret_cast<const float4*>(ks + tt * kDP + row0);
             const float4* q4 = reinterpret_cast<const float4*>(qs + tt * kDP + row0);
-            const float decay = ds[tt], beta = bs[tt], v = vs[tt * 32 + warp * 8 + (lane & 7)];
+            const float decay = ds[tt], beta = bs[tt], kq = kqs[tt], v = vs[tt * 16 + warp * 4 + (lane & 3)];
+            // both read-outs of the state as the previous token left it, S0: with S = g S0 + k u^T,
+            //   S0^T k -> u = beta (v - g S0^T k)   and   S^T q = g S0^T q + u (k . q),
+            // so one butterfly round per token joins both sums and the update is one pass
             float kd[kR];
-            float p[4] = {0.f, 0.f, 0.f, 0.f};
+            float p[4] = {0.f, 0.f, 0.f, 0.f}, o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < kR; r += 4) {
-                const float4 c = k4[r >> 2];
+                const float4 c = k4[r >> 2], a = q4[r >> 2];
                 kd[r] = c.x; kd[r + 1] = c.y; kd[r + 2] = c.z; kd[r + 3] = c.w;
-                S[r] *= decay; S[r + 1] *= decay; S[r + 2] *= decay; S[r + 3] *= decay;
                 p[0] = fmaf(S[r], c.x, p[0]); p[1] = fmaf(S[r + 1], c.y, p[1]); p[2] = fmaf(S[r + 2], c.z, p[2]); p[3] = fmaf(S[r + 3], c.w, p[3]);
-            }
-            const float pred = join4((p[0] + p[1]) + (p[2] + p[3]));
-            const float u = beta * (v - pred);
-            float o[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int r = 0; r < kR; r += 4) {
-                const float4 a = q4[r >> 2];
-                S[r] = fmaf(kd[r], u, S[r]); S[r + 1] = fmaf(kd[r + 1], u, S[r + 1]); S[r + 2] = fmaf(kd[r + 2], u, S[r + 2]); S[r + 3] = fmaf(kd[r + 3], u, S[r + 3]);
                 o[0] = fmaf(S[r], a.x, o[0]); o[1] = fmaf(S[r + 1], a.y, o[1]); o[2] = fmaf(S[r + 2], a.z, o[2]); o[3] = fmaf(S[r + 3], a.w, o[3]);
             }
-            const float ov = join4((o[0] + o[1]) + (o[2] + o[3]));
+            float pk = (p[0] + p[1]) + (p[2] + p[3]), pq = (o[0] + o[1]) + (o[2] + o[3]);
+            join8(pk, pq);
+            const float u = beta * (v - decay * pk);
+            const float ov = fmaf(u, kq, decay * pq);
+#pragma unroll
+            for (int r = 0; r < kR; ++r) S[r] = fmaf(kd[r], u, decay * S[r]);
             if (live && part == 0) out[(int64_t)(first + tt) * H * dv + h * dv + col] = ov;
         }
     }
     if (live) {
+        if (vec) {
 #pragma unroll
-        for (int r = 0; r < kR; ++r)
-            if (row0 + r < dk) Sg[(int64_t)r * dv] = S[r];
+            for (int r = 0; r < kR; r += 4) *reinterpret_cast<float4*>(Sg + r) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
+        } else {
+#pragma unroll
+            for (int r = 0; r < kR; ++r)
+                if (row0 + r < dk) Sg[r] = S[r];
+        }
     }
 }
 
@@ -257,16 +280,16 @@ void gated_delta_rule(const float* qkv, const float* proj, int64_t ld_proj, int3
     B200_REQUIRE(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dk > 0 && dv > 0, kErrBadArg, "gated_delta_rule: bad head counts");
     B200_REQUIRE(dk <= 256, kErrUnsupported, "gated_delta_rule: key size %d > 256", dk);
     cudaStream_t st = as_stream(stream);
-    const dim3 grid(ceil_div(dv, 32), num_heads, num_seqs);
+    const dim3 grid(ceil_div(dv, 16), num_heads, num_seqs);
 #define GDR(R) do { \
-        const int smem = (2 * kTile * 4 * R + kTile * 32 + 2 * kTile) * (int)sizeof(float); \
+        const int smem = (2 * kTile * 8 * R + kTile * 16 + 3 * kTile) * (int)sizeof(float); \
         ensure_dynamic_smem(reinterpret_cast<const void*>(gated_delta_rule_kernel<R>), smem); \
         launch_pdl(gated_delta_rule_kernel<R>, grid, dim3(128), smem, st, qkv, proj, ld_proj, off_b, off_a, A_log, dt_bias, state, out, cu_seqlens, seq_slots, \
                    seq_start, num_heads, num_kv_heads, dk, dv); } while (0)
-    if (dk <= 32) GDR(8);
-    else if (dk <= 64) GDR(16);
-    else if (dk <= 128) GDR(32);
-    else GDR(64);
+    if (dk <= 32) GDR(4);
+    else if (dk <= 64) GDR(8);
+    else if (dk <= 128) GDR(16);
+    else GDR(32);
 #undef GDR
     count_launch();
     check_launch("gated_delta_rule");

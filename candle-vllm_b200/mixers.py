@@ -64,7 +64,7 @@ class GatedDeltaMixer:
         self.w_o = w["o"].to(dtype).contiguous()
 
     def state_shapes(self):
-        return ((max(self.taps - 1, 1), self.C), (self.H, self.dk, self.dv))     # a 1-tap convolution keeps no inputs; one unused row
+        return ((max(self.taps - 1, 1), self.C), (self.H, self.dv, self.dk))     # state stored column-major per head; a 1-tap convolution keeps no inputs; one unused row
 
     def forward(self, h: torch.Tensor, batch: StepBatch, cache) -> torch.Tensor:
         conv_state, S = cache

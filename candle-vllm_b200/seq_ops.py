@@ -122,7 +122,7 @@ def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, conv_state: torch.Tens
 
 def gated_delta_rule(qkv: torch.Tensor, proj: torch.Tensor, off_b: int, off_a: int, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
                      batch: StepBatch, heads: int, kv_heads: int, dk: int, dv: int) -> torch.Tensor:
-    """qkv f32 [T, G dk | G dk | H dv]; b / a read from columns off_b.. / off_a.. of ``proj``; state f32 [slots, H, dk, dv] advanced in place."""
+    """qkv f32 [T, G dk | G dk | H dv]; b / a read from columns off_b.. / off_a.. of ``proj``; state f32 [slots, H, dv, dk] advanced in place."""
     T = qkv.shape[0]
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=qkv.device)
     lib().gated_delta_rule(_ptr(qkv), _ptr(proj), C.c_int64(proj.stride(0) if T > 1 else proj.shape[1]), C.c_int32(off_b), C.c_int32(off_a), _ptr(A_log),

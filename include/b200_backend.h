@@ -423,7 +423,7 @@ void embedding_scaled(const void* table, const int32_t* ids, float* out, int32_t
  *   column multiplies the current token); rows before the portion come from conv_state f32 [slots, K-1, channels] (the sequence's last K-1
  *   inputs), which is then rolled forward over the portion.
  * gated_delta_rule: qkv f32 [T, G dk | G dk | H dv] (the conv output), b and a = columns off_b + h / off_a + h of `proj` (row pitch ld_proj);
- *   per head, state S f32 [slots, H, dk, dv]: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, q and k unit vectors (eps 1e-6,
+ *   per head, state S f32 stored [slots, H, dv, dk] (a column's rows contiguous): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, q and k unit vectors (eps 1e-6,
  *   q also times dk^-1/2), beta = sigmoid(b), g = exp(-exp(A_log[h]) * softplus(a + dt_bias[h])).  out f32 [T, H dv].  dk <= 256.
  * gated_rms_norm: out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[dv] * silu(gate[t, h, :]) (gate row pitch ld_gate). */
 void causal_conv_silu(const float* x, int64_t ldx, const float* taps, float* conv_state, float* y, const int32_t* token_seq,

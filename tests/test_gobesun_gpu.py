@@ -114,7 +114,7 @@ def test_gated_delta_rule(H, Gk, dk, dv):
     decay = torch.exp(-torch.exp(A_log.to(F64)) * torch.nn.functional.softplus(proj[:, 2 + H:2 + 2 * H].to(F64) + dt_bias.to(F64)))
     want = G.delta_recurrence(q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1), v, beta, decay).reshape(T, H * dv)
     for sizes in ([T], [1], [2, 3, 1, 17]):
-        state = torch.full((2, H, dk, dv), 3.0, device=DEV)
+        state = torch.full((2, H, dv, dk), 3.0, device=DEV)
         got = []
         for at, n in _portions(T, sizes):
             b = batch_of([dict(tokens=[0] * n, start=at, block_table=[0, 1], state_slot=1, want=[])])
