@@ -419,7 +419,7 @@ def _lin_io(x: torch.Tensor, n: int, k: int, bias, who: str):
 
 
 class Linear:
-    """Dense 16-bit linear: ``Linear::new(weight [N, K], bias)`` / ``.forward(x)`` (/root/reference/src/openai/models/linear.rs:124-172;
+    """Dense 16-bit linear: ``Linear::new(weight [N, K], bias)`` / ``.forward(x)`` (src/openai/models/linear.rs:124-172;
     the reference reaches cuBLAS through candle's matmul).  f16 or bf16 weights and activations, fp32 accumulation on tcgen05
     (``linear_16bit``, csrc/dense_gemm.cu)."""
 

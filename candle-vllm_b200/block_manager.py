@@ -2,7 +2,7 @@
 ``block_tables`` / ``copy_blocks`` / ``swap_blocks`` inputs of the hot path.
 
 Behavioural mirror of the reference's ``BlockEngine`` and ``PrefixCache``
-(/root/reference/src/scheduler/block_engine.rs:201-1484, /root/reference/src/scheduler/prefix_cache.rs:36-383), written from
+(src/scheduler/block_engine.rs:201-1484, src/scheduler/prefix_cache.rs:36-383), written from
 their observable contract -- the reference's own known-answer tests (block_engine.rs:1537-1751, prefix_cache.rs:401-599) are
 restated in tests/test_block_manager.py and are the parity pin for this file.  Not mirrored: Mamba prefix snapshots and
 image-seeded hashing call sites (the seed hook itself exists), which are outside the decode path.

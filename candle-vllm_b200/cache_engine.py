@@ -1,5 +1,5 @@
 """KV-cache allocator and block-op entry points: mirror of ``CacheEngine``
-(/root/reference/src/scheduler/cache_engine.rs).
+(src/scheduler/cache_engine.rs).
 
   allocate_kv_cache   cache_engine.rs:122-294   (flash layout by default, legacy paged optional)
   shapes              cache_engine.rs:298-341
@@ -30,7 +30,7 @@ class CacheConfig:
 
 
 def kv_head_shard(num_kv_heads: int, rank: int, world: int) -> Tuple[int, int]:
-    """(/root/reference/src/openai/distributed.rs:725-765) -> (local kv heads, first global head)."""
+    """(src/openai/distributed.rs:725-765) -> (local kv heads, first global head)."""
     if world <= 1:
         return num_kv_heads, 0
     if num_kv_heads >= world:

@@ -5,7 +5,7 @@
 // B * ctx * 2 * kvh * 128 * 2 B of KV (537-671 MB at B=32, ctx 4-5k) against ~4 flop/B of math.
 // So the kernel is organised around keeping >= 190 KB of KV reads in flight per SM:
 //   * KV cache = 4-D tensor [num_blocks, 64, kvh, 128] (flash layout,
-//     /root/reference/src/scheduler/cache_engine.rs:326-340); one TMA box {64 dims, 1 head, 32 tokens,
+//     src/scheduler/cache_engine.rs:326-340); one TMA box {64 dims, 1 head, 32 tokens,
 //     1 block} lands a quarter page (4 KB) in shared memory with the 128-byte swizzle, 4 boxes per tile
 //     (K lo/hi, V lo/hi), completion on an mbarrier (cp.async.bulk.tensor -> UTMALDG).
 //   * work item = (sequence, kv head, chunk of <= 8 pages); items are enumerated from the DEVICE-side
@@ -24,7 +24,7 @@
 //     folds the chunks of each (sequence, head), rounds to bf16 and re-zeroes the queue head.
 //
 // Semantics: softmax(q k^T * scale) v over the block table, GQA by head grouping
-// (NaiveAttention::forward /root/reference/src/openai/models/mod.rs:1268-1307; call sites
+// (NaiveAttention::forward src/openai/models/mod.rs:1268-1307; call sites
 // layers/attention.rs:707-718, :983-994; metadata pipelines/inputs.rs:552-568).
 #include <cuda.h>
 

@@ -2,12 +2,12 @@
 //
 // One CTA per (query row, head); warps stride over the context, lanes over head_dim; online softmax
 // in fp32.  This is the catch-all path: both KV layouts (flash and legacy paged,
-// /root/reference/src/scheduler/cache_engine.rs:298-341), FP8(e4m3) caches, softcap, sliding
+// src/scheduler/cache_engine.rs:298-341), FP8(e4m3) caches, softcap, sliding
 // window, any head_dim <= 256.  The TMA-staged split-KV kernel in attention_decode.cu takes over
 // for the flash-layout bf16/f16 decode shapes that dominate the metric.
 //
-// Semantics: NaiveAttention::forward (/root/reference/src/openai/models/mod.rs:1268-1307) over
-// K/V gathered through the block table; metadata /root/reference/src/openai/pipelines/inputs.rs
+// Semantics: NaiveAttention::forward (src/openai/models/mod.rs:1268-1307) over
+// K/V gathered through the block table; metadata src/openai/pipelines/inputs.rs
 // :351-367 (prefill), :552-568 (decode).
 #include "attention.cuh"
 

@@ -1,7 +1,7 @@
 // attention_prefill.cu -- (chunked) prefill attention over the paged KV cache on tensor cores.
 //
-// PagedAttention::forward with is_prefill = true (call sites /root/reference/src/openai/models/layers/attention.rs:707-718, :983-994;
-// metadata /root/reference/src/openai/pipelines/inputs.rs:133-148, :351-367; chunk size 8192, llm_engine.rs:95): varlen causal
+// PagedAttention::forward with is_prefill = true (call sites src/openai/models/layers/attention.rs:707-718, :983-994;
+// metadata src/openai/pipelines/inputs.rs:133-148, :351-367; chunk size 8192, llm_engine.rs:95): varlen causal
 // attention where sequence i owns q rows cu_seqlens_q[i] .. cu_seqlens_q[i+1] = the LAST q_len positions of its k_len context, and
 // ALL keys / values (cached prefix + this chunk) are read from the paged cache the caller has already written.
 //

@@ -3,10 +3,10 @@
 // All three are HBM-bound byte movers: 16-byte vectorised, coalesced accesses, grids sized in
 // multiples of the SM count.  Bit-exact by construction (plain copies / RNE casts).
 //
-// Reference call sites: /root/reference/src/backend/cache.rs:15-165 (copy_blocks),
-// /root/reference/src/scheduler/cache_engine.rs:345-399,527-535 (swap / copy),
-// /root/reference/src/openai/models/layers/attention.rs:707-718,983-994 (cache write inside
-// PagedAttention::forward); slot arithmetic /root/reference/src/openai/pipelines/inputs.rs:410-423.
+// Reference call sites: src/backend/cache.rs:15-165 (copy_blocks),
+// src/scheduler/cache_engine.rs:345-399,527-535 (swap / copy),
+// src/openai/models/layers/attention.rs:707-718,983-994 (cache write inside
+// PagedAttention::forward); slot arithmetic src/openai/pipelines/inputs.rs:410-423.
 #include <algorithm>
 #include <vector>
 
@@ -222,7 +222,7 @@ static void launch_rac(const void* key, const void* value, void* kc, void* vc, c
     }
 }
 
-// FlashInfer-style CSR page tables (indptr / indices / last_len, /root/reference/src/openai/pipelines/inputs.rs:477-506) -> the padded block
+// FlashInfer-style CSR page tables (indptr / indices / last_len, src/openai/pipelines/inputs.rs:477-506) -> the padded block
 // table + context lengths every attention entry point of this library reads.  Device side, no host sync: graph-replay safe.
 __global__ void csr_to_paged_kernel(const uint32_t* __restrict__ indptr, const uint32_t* __restrict__ indices, const uint32_t* __restrict__ last_len,
                                     uint32_t* __restrict__ tables, uint32_t* __restrict__ ctx, int num_seqs, int width, int block_size) {

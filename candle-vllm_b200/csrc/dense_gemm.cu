@@ -1,7 +1,7 @@
 // dense_gemm.cu -- dense 16-bit GEMM on tcgen05:  y[m, n] = sum_k x[m, k] * w[n, k]  (+ bias[n])      x, w f16 or bf16, fp32 accumulate
 //
 // Two users:
-//   * `Linear::forward` on unquantised weights (/root/reference/src/openai/models/linear.rs:124-172; the reference calls cuBLAS through
+//   * `Linear::forward` on unquantised weights (src/openai/models/linear.rs:124-172; the reference calls cuBLAS through
 //     candle's matmul) -- BASELINE config 2 (Llama-3-8B BF16);
 //   * prefill chunks of the weight-only quantised linears (m > 64): the weights are dequantised ONCE into a 16-bit scratch
 //     (dequant_to_16bit below, 2 bytes / weight of extra traffic = ~7 % of the GEMM time at m = 8192) and every m-tile reuses

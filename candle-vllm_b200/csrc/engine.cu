@@ -2,12 +2,12 @@
 // cache, captured once per batch size into a CUDA graph and replayed.
 //
 // Mirrors the reference's host code for this path:
-//   GGUFLLaMa::forward_inner   /root/reference/src/openai/models/quantized_llama.rs:424-506
-//   QuantizedAttention::forward /root/reference/src/openai/models/layers/attention.rs:910-1011
-//   Mlp::forward               /root/reference/src/openai/models/quantized_llama.rs:32-44
-//   GraphCapturer::capture/replay /root/reference/src/backend/graph.rs:471-661, :685-803
+//   GGUFLLaMa::forward_inner   src/openai/models/quantized_llama.rs:424-506
+//   QuantizedAttention::forward src/openai/models/layers/attention.rs:910-1011
+//   Mlp::forward               src/openai/models/quantized_llama.rs:32-44
+//   GraphCapturer::capture/replay src/backend/graph.rs:471-661, :685-803
 //     (static input buffers, metadata copied in, one cuGraphLaunch, stream sync, narrow output)
-//   prepare_decode metadata    /root/reference/src/openai/pipelines/inputs.rs:376-454
+//   prepare_decode metadata    src/openai/pipelines/inputs.rs:376-454
 //
 // Dtype flow (same cast points as the reference): f32 residual stream; QMatMul activations are
 // fp16 (include/b200_backend.h); q,k,v -> bf16 before the cache write / attention; attention output
@@ -521,10 +521,10 @@ b200_llama* b200_llama_create(const b200_llama_config* cfg) {
     m->layers.resize(c.num_layers);
     for (auto& l : m->layers) l = b200_llama_layer_ex{};
     m->heads_l = c.num_heads / c.tp_world;
-    // kv_head_shard (/root/reference/src/openai/distributed.rs:725-765): split, or replicate when kvh < world
+    // kv_head_shard (src/openai/distributed.rs:725-765): split, or replicate when kvh < world
     m->kv_l = c.num_kv_heads >= c.tp_world ? c.num_kv_heads / c.tp_world : 1;
     m->ffn_l = c.ffn / c.tp_world;
-    // pad_vocab_size (/root/reference/src/openai/distributed.rs:1448-1454): multiple of 64, of the world size, of 64 again; every
+    // pad_vocab_size (src/openai/distributed.rs:1448-1454): multiple of 64, of the world size, of 64 again; every
     // rank owns vocab_pad / world rows of the lm_head (rows past `vocab` are padding the caller fills with zeros)
     {
         const int64_t padded = ((int64_t)c.vocab + 63) / 64 * 64;
@@ -553,7 +553,7 @@ b200_llama* b200_llama_create(const b200_llama_config* cfg) {
     char* ws = nullptr;
     ok = ok && dmalloc(ws, m->attn_ws_bytes);
     m->attn_ws = ws;
-    // RoPE tables: calculate_default_inv_freq (/root/reference/src/openai/models/layers/rotary_emb.rs:14-19,31-36)
+    // RoPE tables: calculate_default_inv_freq (src/openai/models/layers/rotary_emb.rs:14-19,31-36)
     const int half = c.head_dim / 2;
     std::vector<float> hc((size_t)c.max_pos * half), hs((size_t)c.max_pos * half);
     for (int i = 0; i < half; ++i) {
@@ -730,7 +730,7 @@ void b200_llama_set_comm(b200_llama* m, void* nccl_comm) {
 }
 
 // full-vocabulary logits [n, vocab] on the device: the local buffer at TP = 1; vocab-parallel (VocabParallelLinear::forward,
-// /root/reference/src/openai/distributed.rs:1632-1667): all-gather the [n, vocab_l] shards -> [world, n, vocab_l] -> transpose ->
+// src/openai/distributed.rs:1632-1667): all-gather the [n, vocab_l] shards -> [world, n, vocab_l] -> transpose ->
 // [n, world * vocab_l] -> narrow to the original vocab.  A collective: every rank must ask for logits in the same step.
 static const float* full_logits(b200_llama* m, int n, cudaStream_t st) {
     if (m->cfg.tp_world == 1) return m->logits;

@@ -1,7 +1,7 @@
 // fp_linear.cu -- weight-only low-precision float linears: block-scaled FP8 (e4m3), NVFP4 and MXFP4.
 //
 // Reference call sites (the kernels themselves live in attention-rs, not in the reference tree):
-//   LnFp8::forward   -> attention_rs::fp8_linear::fp8_matmul      /root/reference/src/openai/models/linear.rs:1190-1221
+//   LnFp8::forward   -> attention_rs::fp8_linear::fp8_matmul      src/openai/models/linear.rs:1190-1221
 //       weight e4m3 [N,K], weight_scale f32 [ceil(N/by), ceil(K/bx)] multiplies the tile (linear.rs:944-973)
 //   LnNvfp4::forward -> attention_rs::nvfp4_linear::nvfp4_matmul  linear.rs:1913-1943
 //       blocks u8 [N,K/2] (two e2m1 per byte, low nibble = even k), scales e4m3 [N,K/16], global_scale f32 (:1821-1853)

@@ -2,7 +2,7 @@
 //
 //     wo  ->  [+residual, RMSNorm]  ->  gate|up  ->  [SiLU * up]  ->  w2  ->  [+residual, RMSNorm]  ->  QKV of the next layer
 //
-// (GGUFLLaMa::forward_inner /root/reference/src/openai/models/quantized_llama.rs:424-506, Mlp::forward :32-44,
+// (GGUFLLaMa::forward_inner src/openai/models/quantized_llama.rs:424-506, Mlp::forward :32-44,
 // QuantizedAttention::forward layers/attention.rs:910-1011; tensor parallel: AllReduce after the row-parallel linears,
 // distributed.rs:572-653, :696-710).
 //

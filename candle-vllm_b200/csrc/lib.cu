@@ -4,6 +4,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <map>
 #include <set>
 #include <utility>
 
@@ -58,12 +59,13 @@ int sm_count() {
 
 void ensure_dynamic_smem(const void* kernel, int bytes) {
     static std::mutex mu;
-    static std::set<std::pair<int, const void*>> done;
+    static std::map<std::pair<int, const void*>, int> done;      // the largest size a kernel was opened for, per device
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return; }
     std::lock_guard<std::mutex> lk(mu);
-    if (done.count({dev, kernel})) return;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess) done.insert({dev, kernel});
+    auto it = done.find({dev, kernel});
+    if (it != done.end() && it->second >= bytes) return;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess) done[{dev, kernel}] = bytes;
     else cudaGetLastError();
 }
 

@@ -1,6 +1,6 @@
 // marlin_api.cu -- C ABI of the GPTQ / Marlin int4 weight-only GEMM: replaces attention_rs::kernels::ffi::
-// {gptq_repack, marlin_4bit_f16, marlin_4bit_bf16} (call sites /root/reference/src/backend/gptq.rs:115-178, :313-332;
-// host-side preparation /root/reference/src/openai/models/linear.rs:300-413).
+// {gptq_repack, marlin_4bit_f16, marlin_4bit_bf16} (call sites src/backend/gptq.rs:115-178, :313-332;
+// host-side preparation src/openai/models/linear.rs:300-413).
 //
 // gptq_repack turns the GPTQ checkpoint layout (u32 [K/8, N], 8 nibbles along K per word) into this library's
 // row-major int4 layout (same number of words; only marlin_4bit_* reads it, so the layout is private to the
@@ -58,7 +58,7 @@ __global__ void awq_repack_kernel(const uint32_t* __restrict__ in, uint32_t* __r
     }
 }
 
-// Marlin checkpoint format (`B` u32 [K/16, 2N], checkpoint_format == "marlin", /root/reference/src/openai/models/linear.rs:219-251) -> GPTQ packing
+// Marlin checkpoint format (`B` u32 [K/16, 2N], checkpoint_format == "marlin", src/openai/models/linear.rs:219-251) -> GPTQ packing
 // u32 [K/8, N], from which gptq_repack makes this library's layout.  The tile order is the Marlin project's published one (IST-DASLab/marlin,
 // `_get_perms` / `Layer.pack`): w[k][n] sits in row k / 16, tile-flat position (n / 16) * 256 + (k % 16) * 16 + n % 16,
 // permuted inside every 1024 values by `perm` (inv_perm below, built once on the host) and packed 8 nibbles per word with stride 8.
@@ -104,7 +104,7 @@ static bool upload_marlin_inv_perm() {
 }
 
 // Conventional GPTQ (act-order and / or asymmetric, 4 or 8 bit): the shape-generic path behind gemm_half_q_half_alt
-// (call site /root/reference/src/backend/gptq.rs:182-197).  qweight [K / pack, N] packed along K, qzeros [G, N / pack] packed
+// (call site src/backend/gptq.rs:182-197).  qweight [K / pack, N] packed along K, qzeros [G, N / pack] packed
 // along N and stored minus one (GPTQ v1), scales f16 [G, N], group of row k = g_idx[k].  One thread per output column
 // (coalesced weight words), 8 activation rows per pass, fp32 accumulation, f16 output.
 template <int kBits>

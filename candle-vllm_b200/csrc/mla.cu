@@ -1,7 +1,7 @@
 // mla.cu -- multi-head latent attention over the paged latent cache (DeepSeek-V2/V3, BASELINE config 5).
 //
 // Replaces attention_rs::mla::{concat_and_cache_mla, mla_paged_decode, mla_paged_prefill} as called from
-// /root/reference/src/openai/models/layers/mla_attention.rs:479-552; cache shapes /root/reference/src/scheduler/cache_engine.rs:172-185:
+// src/openai/models/layers/mla_attention.rs:479-552; cache shapes src/scheduler/cache_engine.rs:172-185:
 //   ckv_cache [num_blocks, block_size, 1, kv_lora_rank = 512], kpe_cache [num_blocks, block_size, 1, qk_rope_head_dim = 64] (model dtype).
 // "Absorbed" formulation: the caller has folded W_uk into q (q_absorbed [T, H, 512]) and applies W_uv to the result, so attention runs in
 // the latent space: score(t) = (q_abs . ckv_t + q_pe . kpe_t) * sm_scale, out = sum_t softmax(score)_t ckv_t  -> [T, H, 512].

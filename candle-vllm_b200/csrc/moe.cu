@@ -1,6 +1,6 @@
 // moe.cu -- fused mixture-of-experts path on GGUF expert tensors: top-k routing, expert sort and the grouped
 // dequant-GEMM.  Mirrors the reference's FusedMoe::forward over attention_rs::{topk::topk_softmax, moe::moe_gemm_gguf}
-// (/root/reference/src/openai/models/layers/moe.rs:35-45, :425-480, :1429-1482; quantized_qwen3_moe.rs:70-141; BASELINE config 4:
+// (src/openai/models/layers/moe.rs:35-45, :425-480, :1429-1482; quantized_qwen3_moe.rs:70-141; BASELINE config 4:
 // Qwen3-30B-A3B Q4_K, 128 experts, top-8).
 //
 //   topk_softmax            softmax over the router logits of a token, the k largest probabilities and their expert ids
@@ -298,7 +298,7 @@ size_t moe_gemm_fp8_workspace_bytes(int32_t num_pairs, int32_t n, int32_t k, int
     return moe_gemm_workspace_bytes(num_pairs, n, k, num_experts) + ((size_t)num_pairs * (size_t)n * 4 + 255) / 256 * 256 + 256;
 }
 
-// attention_rs::moe::moe_gemm_fp8 (call sites /root/reference/src/openai/models/layers/moe.rs:1447-1473): x [size_m, k] and out [num_pairs, n] of
+// attention_rs::moe::moe_gemm_fp8 (call sites src/openai/models/layers/moe.rs:1447-1473): x [size_m, k] and out [num_pairs, n] of
 // `dtype` (f16 / bf16); experts e4m3 [E, n, k]; scale f32 [E, ceil(n / by), ceil(k / bx)]; the rest as moe_gemm_gguf.
 void moe_gemm_fp8(const void* x, const void* experts, const float* scale, const float* topk_weights, const uint32_t* sorted_token_ids,
                   const uint32_t* expert_ids, void* out, int32_t num_experts, int32_t topk, int32_t size_m, int32_t num_pairs, int32_t n, int32_t k,

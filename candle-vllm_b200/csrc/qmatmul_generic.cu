@@ -6,7 +6,7 @@
 // decode hot path.  Activations are rounded to fp16 first so both paths share one numerical
 // contract (see include/b200_backend.h).
 //
-// Reference call sites: QMatMul::forward /root/reference/src/openai/models/linear.rs:765-806;
+// Reference call sites: QMatMul::forward src/openai/models/linear.rs:765-806;
 // QTensor::dequantize linear.rs:808-842.
 #include "qmatmul.cuh"
 

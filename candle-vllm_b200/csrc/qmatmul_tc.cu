@@ -22,7 +22,7 @@
 //     written to per-CTA slabs (deterministic mode; the 16-bit-output GEMMs add a finishing pass).
 // Measured behaviour, fixes and dead ends: DESIGN.md 4.2, profiles/r01_qmatmul_tc_ncu.md.
 //
-// Reference semantics: QMatMul::forward (/root/reference/src/openai/models/linear.rs:765-806); block formats SURVEY.md
+// Reference semantics: QMatMul::forward (src/openai/models/linear.rs:765-806); block formats SURVEY.md
 // Appendix A.  The reference's CUDA path quantises activations to Q8_1 and uses dp4a; here activations are fp16 and
 // accumulation fp32 (strictly closer to the fp32 target).
 #include <cuda.h>
@@ -110,7 +110,7 @@ __device__ __forceinline__ int seg_first_tile(const GemmParams& p, int sg) { ret
 // Symmetric int4 (GPTQ) in the repacked layout written by gptq_repack(): per row, per 64-k chunk, 32 bytes whose low
 // nibbles are k = 0..31 and high nibbles k = 32..63 of the chunk -- the same nibble geometry as a Q4_K chunk, so the
 // subnormal-placement + HFMA2 trick applies unchanged: w = s*q - 8*s with one per-group scale s
-// (/root/reference/src/backend/gptq.rs:115-178 call site; scales arrive marlin-permuted, linear.rs:341-379).
+// (src/backend/gptq.rs:115-178 call site; scales arrive marlin-permuted, linear.rs:341-379).
 struct M4Ctx { const void* scales; int n_total, group_size, k0, n_idx, bf16, dbg, by, sk; const float* norm; const uint32_t* zp;
                float pre[4]; int has_pre; };   // int4: {s0, s1, z0, z1} of this thread's quarter, loaded one unit ahead by the caller   // by / sk: fp8 scale-tile rows, scale columns; norm: fp8 range shift; zp: AWQ zero points (marlin layout) or null
 __device__ __forceinline__ int marlin_scale_pos(int n, bool grouped) {

@@ -1,5 +1,5 @@
 // tp.cu -- tensor-parallel collectives on the residual path (AllReduce after the row-parallel
-// o_proj / down_proj: /root/reference/src/openai/distributed.rs:547-654, :696-710).
+// o_proj / down_proj: src/openai/distributed.rs:547-654, :696-710).
 // NCCL is resolved at run time from the already-loaded torch-bundled libnccl.so.2 (the host
 // process creates the communicator); no link-time dependency.
 #include <dlfcn.h>
@@ -25,7 +25,7 @@ static bool resolve() {
     return g_allreduce != nullptr && g_allgather != nullptr;
 }
 
-// VocabParallelLinear + AllGather (/root/reference/src/openai/distributed.rs:1632-1667) reduced to what greedy
+// VocabParallelLinear + AllGather (src/openai/distributed.rs:1632-1667) reduced to what greedy
 // decoding needs: every rank contributes (max logit, global index) per sequence; gather 8 bytes per sequence.
 void tp_allgather_bytes(void* comm, const void* src, void* dst, size_t bytes_per_rank, cudaStream_t st) {
     if (!comm) { set_error(kErrBadArg, "tp_allgather: no communicator"); return; }
@@ -44,7 +44,7 @@ void tp_allreduce_f32(void* comm, float* buf, int64_t n, cudaStream_t st) {
 
 // ---- fused all-reduce over NVLink peer memory ------------------------------------------------------------------------
 // Replaces {zero partial, GEMM, ncclAllReduce, add, rms_norm} of the row-parallel linears by {GEMM, this kernel}
-// (reference semantics: AllReduce::cuda_fwd + residual add + RmsNorm, /root/reference/src/openai/distributed.rs:572-653,
+// (reference semantics: AllReduce::cuda_fwd + residual add + RmsNorm, src/openai/distributed.rs:572-653,
 // quantized_llama.rs:470-488).  Two hops over NVLink / NVSwitch, no fences, no separate flags:
 //   * token row r is OWNED by rank r % world: only the owner keeps the fp32 residual stream of that row;
 //   * hop 1 (reduce): every other rank pushes its partial row into the owner's gather slot as {value, epoch} 8-byte words

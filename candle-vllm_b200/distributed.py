@@ -1,7 +1,7 @@
 """Tensor-parallel plumbing: one process per GPU, ``torch.distributed`` for rendezvous, a raw NCCL
 communicator (torch-bundled libnccl.so.2, via ctypes) handed to the C++ engine for the residual-path
-all-reduce.  Mirrors ``Comm::from_rank`` (/root/reference/src/openai/pipelines/pipeline.rs:805-812)
-and ``AllReduce`` (/root/reference/src/openai/distributed.rs:547-654); the NCCL unique id travels
+all-reduce.  Mirrors ``Comm::from_rank`` (src/openai/pipelines/pipeline.rs:805-812)
+and ``AllReduce`` (src/openai/distributed.rs:547-654); the NCCL unique id travels
 over the host control plane (reference: env/TCP, communicator.rs:218-324; here: torch.distributed).
 """
 from __future__ import annotations

@@ -1,6 +1,6 @@
 """Serving loop for ragged-step models: the step function (``ModelRunner.execute``), the request scheduler with chunked prefill and
 continuous batching, and ``LLMEngine.generate``.  Roles follow the reference's ``LLMEngine`` + ``Scheduler``
-(/root/reference/src/openai/pipelines/llm_engine.rs, /root/reference/src/scheduler/mod.rs): waiting -> running queues, a token budget per
+(src/openai/pipelines/llm_engine.rs, src/scheduler/mod.rs): waiting -> running queues, a token budget per
 step, blocks from ``BlockManager``, recurrent-state slots from ``StateCache``; unlike the reference a step may carry prompt portions
 and decoded tokens together.
 
@@ -26,7 +26,7 @@ from .state_cache import StateCache
 
 class _DecodeGraph:
     """A captured step of B single-token entries (the reference replays captured decode graphs the same way,
-    /root/reference/src/backend/graph.rs:685-803): static metadata buffers, two small H2D copies and one graph launch per step.
+    src/backend/graph.rs:685-803): static metadata buffers, two small H2D copies and one graph launch per step.
     Warm-up runs on a scratch state slot with the cache write switched off, so capturing disturbs no live sequence."""
 
     def __init__(self, runner: "ModelRunner", B: int, width: int):

@@ -1,5 +1,5 @@
 """Metadata builder: mirror of ``LLMEngine::prepare_decode`` / ``prepare_prompt``
-(/root/reference/src/openai/pipelines/inputs.rs:90-374, :376-575) for plain sequences.
+(src/openai/pipelines/inputs.rs:90-374, :376-575) for plain sequences.
 
 Pure host-side integer logic (numpy); ``to_device`` wraps the result into the ``InputMetadata`` the
 kernels consume (5 small H2D copies per step, like the reference).

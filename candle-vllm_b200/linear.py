@@ -1,4 +1,4 @@
-"""``QLinear``: the reference's dispatch over quantised linears (/root/reference/src/openai/models/linear.rs:419-916).
+"""``QLinear``: the reference's dispatch over quantised linears (src/openai/models/linear.rs:419-916).
 
 GPTQ / AWQ tuple (scales present) -> ``gptq_matmul``; GGUF tensor -> ``QMatMul`` on f32-cast activations (``forward_no_dequant``,
 f32 result); GGUF tensor stored transposed -> dequantise to f16 and a plain (cuBLAS) matmul (``forward_via_dequant``).

@@ -35,7 +35,7 @@ class LlamaConfig:
 
 
 def padded_vocab(vocab: int, world: int) -> int:
-    """pad_vocab_size (/root/reference/src/openai/distributed.rs:1448-1454); identity at world 1."""
+    """pad_vocab_size (src/openai/distributed.rs:1448-1454); identity at world 1."""
     if world == 1:
         return vocab
     padded = -(-vocab // 64) * 64

@@ -1,5 +1,5 @@
 """Multi-head latent attention over the paged latent cache: mirror of the attention-rs MLA calls made by ``MlaAttention::forward``
-(/root/reference/src/openai/models/layers/mla_attention.rs:479-552) over the C ABI (``concat_and_cache_mla``, ``mla_paged_attention``)."""
+(src/openai/models/layers/mla_attention.rs:479-552) over the C ABI (``concat_and_cache_mla``, ``mla_paged_attention``)."""
 from __future__ import annotations
 
 import ctypes as C

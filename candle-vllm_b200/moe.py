@@ -1,5 +1,5 @@
 """Fused mixture-of-experts on GGUF expert tensors: mirror of ``FusedMoe`` (GGUF flavour,
-/root/reference/src/openai/models/layers/moe.rs:1429-1482; quantized_qwen3_moe.rs:70-141) over the C ABI
+src/openai/models/layers/moe.rs:1429-1482; quantized_qwen3_moe.rs:70-141) over the C ABI
 (``topk_softmax``, ``sort_expert_assignments``, ``moe_gemm_gguf``)."""
 from __future__ import annotations
 

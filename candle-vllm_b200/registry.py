@@ -1,5 +1,5 @@
 """Model registry: ``config.json`` -> model class, the way the reference picks a pipeline from the ``architectures`` entry of a
-checkpoint (/root/reference/src/openai/pipelines/pipeline.rs, ``get_arch_cfg``).  A model class offers
+checkpoint (src/openai/pipelines/pipeline.rs, ``get_arch_cfg``).  A model class offers
 ``from_pretrained(path, dtype=..., block_size=..., max_pos=...)``, ``cache_plan()`` and ``forward(batch, kv_cache, state_cache)``."""
 from __future__ import annotations
 

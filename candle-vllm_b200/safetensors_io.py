@@ -1,6 +1,6 @@
 """Reader for safetensors checkpoints: an 8-byte little-endian header length, that many bytes of JSON (tensor name -> dtype, shape,
 data_offsets into the rest of the file), then the raw little-endian data.  The reference loads its unquantised models through the
-safetensors crate (/root/reference/src/openai/models/mod.rs, `VarBuilder::from_mmaped_safetensors`); this is the same format read
+safetensors crate (src/openai/models/mod.rs, `VarBuilder::from_mmaped_safetensors`); this is the same format read
 with numpy's memory map, one tensor at a time, so a checkpoint larger than host memory can stream to the device."""
 from __future__ import annotations
 

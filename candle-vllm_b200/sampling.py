@@ -1,5 +1,5 @@
 """Token sampling: greedy on the device (``argmax_f32``), everything else on the host from the step's f32 logits, like the reference's
-``LogitsProcessor`` (/root/reference/src/openai/sampling_params.rs, src/openai/logits_processor.rs: temperature, top-k, top-p, seeded)."""
+``LogitsProcessor`` (src/openai/sampling_params.rs, src/openai/logits_processor.rs: temperature, top-k, top-p, seeded)."""
 from __future__ import annotations
 
 from dataclasses import dataclass, field

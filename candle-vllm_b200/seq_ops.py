@@ -45,6 +45,7 @@ class StepBatch:
     num_want: int = 0
     max_position: int = 0
     pure_decode: bool = False     # every entry brings exactly one token
+    max_rows: int = 1             # the most rows any entry brings
 
     @classmethod
     def from_host(cls, prep: dict, device="cuda") -> "StepBatch":
@@ -54,7 +55,8 @@ class StepBatch:
                    seq_slots=t(prep["seq_slots"], np.int32), seq_start=t(prep["seq_start"], np.int32),
                    block_tables=t(prep["block_tables"], np.int32), want_rows=t(prep["want_rows"], np.int32),
                    num_tokens=len(prep["tokens"]), num_seqs=len(prep["seq_slots"]), num_want=len(prep["want_rows"]),
-                   max_position=int(prep["max_position"]), pure_decode=len(prep["tokens"]) == len(prep["seq_slots"]))
+                   max_position=int(prep["max_position"]), pure_decode=len(prep["tokens"]) == len(prep["seq_slots"]),
+                   max_rows=int(np.diff(np.asarray(prep["cu_seqlens"], np.int64)).max()) if len(prep["seq_slots"]) else 1)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -120,12 +122,28 @@ def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, conv_state: torch.Tens
     return y
 
 
+TILED_DELTA_MIN_ROWS = 8      # steps in which some entry brings at least this many rows take the tiled form of the rule
+
+
 def gated_delta_rule(qkv: torch.Tensor, proj: torch.Tensor, off_b: int, off_a: int, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
-                     batch: StepBatch, heads: int, kv_heads: int, dk: int, dv: int) -> torch.Tensor:
-    """qkv f32 [T, G dk | G dk | H dv]; b / a read from columns off_b.. / off_a.. of ``proj``; state f32 [slots, H, dv, dk] advanced in place."""
+                     batch: StepBatch, heads: int, kv_heads: int, dk: int, dv: int, tiled: Optional[bool] = None) -> torch.Tensor:
+    """qkv f32 [T, G dk | G dk | H dv]; b / a read from columns off_b.. / off_a.. of ``proj``; state f32 [slots, H, dv, dk] advanced in place.
+    Two kernels compute the same rule: token by token (single decoded tokens, short portions), and over tiles of 16 tokens (portions of
+    prompts; key sizes up to 128).  ``tiled`` forces one of them; None chooses by the longest portion of the step."""
     T = qkv.shape[0]
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=qkv.device)
-    lib().gated_delta_rule(_ptr(qkv), _ptr(proj), C.c_int64(proj.stride(0) if T > 1 else proj.shape[1]), C.c_int32(off_b), C.c_int32(off_a), _ptr(A_log),
+    ld_proj = C.c_int64(proj.stride(0) if T > 1 else proj.shape[1])
+    if tiled is None:
+        tiled = dk <= 128 and batch.max_rows >= TILED_DELTA_MIN_ROWS
+    if tiled:
+        scratch = torch.empty((T * (2 * kv_heads * dk + 35 * heads),), dtype=torch.float32, device=qkv.device)
+        lib().gated_delta_rule_tiled(_ptr(qkv), _ptr(proj), ld_proj, C.c_int32(off_b), C.c_int32(off_a), _ptr(A_log), _ptr(dt_bias), _ptr(state), _ptr(out),
+                                     _ptr(scratch), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(T),
+                                     C.c_int32(batch.num_seqs), C.c_int32(batch.max_rows), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk),
+                                     C.c_int32(dv), _stream(qkv.device))
+        check("gated_delta_rule_tiled")
+        return out
+    lib().gated_delta_rule(_ptr(qkv), _ptr(proj), ld_proj, C.c_int32(off_b), C.c_int32(off_a), _ptr(A_log),
                            _ptr(dt_bias), _ptr(state), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start),
                            C.c_int32(batch.num_seqs), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk), C.c_int32(dv), _stream(qkv.device))
     check("gated_delta_rule")

@@ -1,6 +1,6 @@
 """Recurrent-state storage beside the paged KV cache: fixed-size per-sequence state lives in *slots*, one slot per live sequence,
 handed out and taken back like KV blocks.  The reference keeps the analogous Mamba state pool next to its block engine
-(/root/reference/src/scheduler/block_engine.rs, "mamba" snapshots); here a slot is an ``int`` and the pool a FIFO free list, the same
+(src/scheduler/block_engine.rs, "mamba" snapshots); here a slot is an ``int`` and the pool a FIFO free list, the same
 representation ``BlockManager`` uses for blocks.
 
 A slot is NOT cleared when it changes hands: every kernel that reads state is told whether its entry starts a sequence

@@ -5,7 +5,7 @@ Q4_K: 12 scale bytes + 128 nibble bytes uniform, d ~ U(0.5,2)*2^-14, dmin ~ 7.5*
 (zero-mean weights of std ~0.02, so activations stay O(1) through 32 layers); Q6_K: 208 bytes
 uniform, d ~ U(0.5,2)*2^-16.  Norm weights ~ U(0.5,1.5), embeddings N(0,1).
 Tensor-parallel shards follow the reference: column split dim 0, row split dim 1 by raw blocks
-(/root/reference/src/openai/models/layers/quantized_var_builder.rs:234-269).
+(src/openai/models/layers/quantized_var_builder.rs:234-269).
 """
 from __future__ import annotations
 
@@ -85,7 +85,7 @@ def make_weights(cfg: LlamaConfig, device="cuda", seed: int = 0, tp_rank: int = 
     row = (lambda w: shard_cols(w, tp_rank, tp_world)) if tp_world > 1 else (lambda w: w)
     kcol = col
     if tp_world > 1 and cfg.num_kv_heads < tp_world:
-        # kv_head_shard with fewer kv heads than ranks (/root/reference/src/openai/distributed.rs:753-764): every rank holds ONE
+        # kv_head_shard with fewer kv heads than ranks (src/openai/distributed.rs:753-764): every rank holds ONE
         # kv head, replicated over world / kvh consecutive ranks
         if tp_world % cfg.num_kv_heads:
             raise ValueError(f"world {tp_world} not a multiple of {cfg.num_kv_heads} kv heads")

@@ -4,9 +4,9 @@
  *
  * Conventions (identical to the reference's `attention_rs::kernels::ffi`):
  *   - extern "C", plain pointers and sizes, `int64_t stream` = the caller's CUstream
- *     (`*dev.cu_stream() as i64`, /root/reference/src/backend/cache.rs:135, gptq.rs:130);
+ *     (`*dev.cu_stream() as i64`, src/backend/cache.rs:135, gptq.rs:130);
  *   - every entry point is stream-ordered, allocation-free, host-sync-free and therefore
- *     CUDA-graph capture safe (/root/reference/src/backend/graph.rs:271-274); scratch memory is
+ *     CUDA-graph capture safe (src/backend/graph.rs:271-274); scratch memory is
  *     a caller-provided `workspace` whose size comes from the matching `*_workspace_bytes`;
  *   - functions return void like the reference's; argument errors (the reference validates on the
  *     Rust side and `bail!`s, cache.rs:26-39, gptq.rs:232-238) are recorded per thread and read
@@ -44,12 +44,12 @@ enum { B200_F32 = 0, B200_F16 = 1, B200_BF16 = 2, B200_U8 = 3, B200_FP8_E4M3 = 4
        B200_F16_K4 = 5 };
 /* GGML tensor types (values = ggml_type, as stored in GGUF files) */
 enum { B200_GGML_Q8_0 = 8, B200_GGML_Q4_K = 12, B200_GGML_Q6_K = 14 };
-/* KV layouts (/root/reference/src/scheduler/cache_engine.rs:298-341) */
+/* KV layouts (src/scheduler/cache_engine.rs:298-341) */
 enum { B200_KV_FLASH = 0 /* K,V [nb, bs, kvh, hd] */,
        B200_KV_PAGED = 1 /* K [nb, kvh, hd/x, bs, x], V [nb, kvh, hd, bs], x = 16/elem */ };
 
 /* ---- K4: copy_blocks -- replaces attention_rs::kernels::ffi::copy_blocks_{bf16,f16,f32} ----
- * Call site: /root/reference/src/backend/cache.rs:127-162.  The first three arguments are HOST
+ * Call site: src/backend/cache.rs:127-162.  The first three arguments are HOST
  * pointers (Vec::as_mut_ptr, cache.rs:112-114): u64 device addresses of each layer's K / V cache,
  * and i64 (src,dst) block pairs.  For every layer, K and V: dst block <- src block,
  * numel_per_block elements each.  copy_blocks_u8 adds the arm the reference lacks for FP8 KV
@@ -64,7 +64,7 @@ void copy_blocks_u8  (void* key_cache_ptrs, void* value_cache_ptrs, const void* 
                       int32_t num_layers, int32_t num_pairs, int32_t numel_per_block, int64_t stream);
 
 /* ---- K5: swap_blocks -- replaces attention_rs::cache::swap_blocks(src, dst, &HashMap) -------
- * Call site: /root/reference/src/scheduler/cache_engine.rs:527-535 (swap_in :345-363, swap_out
+ * Call site: src/scheduler/cache_engine.rs:527-535 (swap_in :345-363, swap_out
  * :365-385).  dst[dst_block] <- src[src_block], bytes_per_block each.  `mapping` is a HOST array
  * of i64 (src,dst) pairs.  One of src/dst may be host memory (pinned or pageable); the copy kind
  * is inferred (cudaMemcpyDefault).  Adjacent pairs are coalesced into single copies. */
@@ -72,15 +72,15 @@ void swap_blocks(const void* src, void* dst, const int64_t* mapping, int32_t num
                  int64_t bytes_per_block, int64_t stream);
 
 /* ---- FlashInfer-style page tables (the reference's default build): indptr u32 [B + 1], indices u32 [nnz] (physical block ids, sequence by
- * sequence), last_len u32 [B] (tokens in each sequence's last page), as built at /root/reference/src/openai/pipelines/inputs.rs:477-506 ->
+ * sequence), last_len u32 [B] (tokens in each sequence's last page), as built at src/openai/pipelines/inputs.rs:477-506 ->
  * block_tables u32 [B, max_blocks_per_seq] (0-padded) and context_lens u32 [B] = (pages - 1) * block_size + last_len (inputs.rs:523-531), on
  * the device and stream-ordered, so a host that only has CSR metadata (graph.rs:471-803 static buffers) can drive every entry point below. */
 void flashinfer_csr_to_paged(const uint32_t* indptr, const uint32_t* indices, const uint32_t* last_len, uint32_t* block_tables, uint32_t* context_lens,
                              int32_t num_seqs, int32_t max_blocks_per_seq, int32_t block_size, int64_t stream);
 
 /* ---- K3: reshape_and_cache -- the cache write inside PagedAttention::forward ----------------
- * Call sites: /root/reference/src/openai/models/layers/attention.rs:707-718, :983-994; slot math
- * /root/reference/src/openai/pipelines/inputs.rs:180-194, :410-423.
+ * Call sites: src/openai/models/layers/attention.rs:707-718, :983-994; slot math
+ * src/openai/pipelines/inputs.rs:180-194, :410-423.
  * key/value: [num_tokens, num_kv_heads, head_dim] of `in_dtype` (B200_F32/F16/BF16), row strides
  * in elements.  slot_mapping i64[num_tokens]: flat slot = block*block_size + offset; negative
  * (pad, -1) = skip.  cache_dtype: same 16-bit type as the model dtype, or B200_FP8_E4M3 (stored as
@@ -91,7 +91,7 @@ void reshape_and_cache(const void* key, const void* value, void* key_cache, void
                        int32_t in_dtype, int32_t cache_dtype, int32_t layout, int64_t stream);
 
 /* ---- K1: paged attention, decode -- PagedAttention::forward with is_prefill = false ---------
- * Call sites as above; metadata contract /root/reference/src/openai/pipelines/inputs.rs:552-568.
+ * Call sites as above; metadata contract src/openai/pipelines/inputs.rs:552-568.
  * q, out: [num_seqs, num_heads, head_dim] of `dtype` (B200_BF16 / B200_F16), contiguous.
  * block_tables u32 [num_seqs, max_blocks_per_seq] (0-padded), context_lens u32 [num_seqs]
  * INCLUDING the token being decoded.  The kernel reads only device-side context_lens (never a
@@ -111,7 +111,7 @@ void paged_attention_decode(void* out, const void* q, const void* key_cache, con
                             void* workspace, size_t workspace_bytes, int64_t stream);
 
 /* ---- K2: paged attention, (chunked) prefill -- is_prefill = true ----------------------------
- * Metadata /root/reference/src/openai/pipelines/inputs.rs:133-148, :351-367.  Varlen causal
+ * Metadata src/openai/pipelines/inputs.rs:133-148, :351-367.  Varlen causal
  * attention; ALL keys/values (cached prefix + this chunk) are read from the paged cache, which the
  * caller has already written with reshape_and_cache.  Sequence i owns q rows
  * cu_seqlens_q[i]..cu_seqlens_q[i+1] = the last q_len positions of its k_len context. */
@@ -124,8 +124,8 @@ void paged_attention_prefill(void* out, const void* q, const void* key_cache, co
                              int32_t dtype, int32_t cache_dtype, int32_t layout, int64_t stream);
 
 /* ---- K6: QMatMul::forward on GGUF tensors -- replaces candle QMatMul (quantized.cu) ---------
- * Call sites: /root/reference/src/openai/models/linear.rs:765-806,
- * /root/reference/src/openai/models/quantized_llama.rs:33-37, layers/attention.rs:920-922,1004.
+ * Call sites: src/openai/models/linear.rs:765-806,
+ * src/openai/models/quantized_llama.rs:33-37, layers/attention.rs:920-922,1004.
  * y[m,n] (f32) = x[m,k] (f32) . dequant(W[n,k])^T.  W = GGML blocks, row-major over n, verbatim
  * GGUF bytes (k % 256 == 0 for K-quants, % 32 for Q8_0).  Activations are rounded to fp16
  * (saturating) and products accumulate in fp32 on the tensor cores; the reference quantises
@@ -155,11 +155,11 @@ void dequantize_f32(const void* w, float* out, int64_t n, int64_t k, int32_t ggm
 
 /* ---- K7 / K9: GPTQ -> Marlin int4 weight-only GEMM -- replaces attention_rs::kernels::ffi::{gptq_repack,
  * marlin_4bit_f16, marlin_4bit_bf16, marlin_awq_4bit_*, awq_repack, gemm_half_q_half_alt} with the reference's exact
- * signatures (/root/reference/src/backend/gptq.rs:115-197, :313-332).
+ * signatures (src/backend/gptq.rs:115-197, :313-332).
  * gptq_repack: qweight u32 [k_packed = K/8, n] (8 nibbles along K per word) -> same word count in this library's
  *   private int4 layout (the reference reshapes the result to [K/16, 2n], gptq.rs:283-297; only marlin_4bit_* reads it).
  * marlin_4bit_{f16,bf16}: out[m,n] = x[m,k] . ((q - 8) * scale)^T; scales [k/group, n] in the order produced by the
- *   reference's marlin_permute_scales (/root/reference/src/openai/models/linear.rs:354-379); qzeros ignored (symmetric),
+ *   reference's marlin_permute_scales (src/openai/models/linear.rs:354-379); qzeros ignored (symmetric),
  *   g_idx is accepted and NOT read (the reference passes the checkpoint's trivial k / group_size sequence on this path, linear.rs:298-337;
  *   act-order goes to gemm_half_q_half_alt); group_size 64 / 128 / -1; k % 256 == 0; n % 64 == 0; any m (64 rows per tensor-core pass).  `workspace` (n zeroed u32 of
  *   locks in Marlin) is unused.  The fp16 copy of x lives in a library-owned scratch buffer per (device, stream), grown outside
@@ -190,13 +190,13 @@ void gemm_half_q_half_alt(const void* x, const uint32_t* qweight, const uint32_t
                           const int32_t* g_idx, void* out, int32_t m, int32_t n, int32_t k, int32_t bits, int64_t stream);
 void b200_set_scratch(void* device_ptr, size_t bytes);
 
-/* ---- dense 16-bit Linear::forward -- replaces candle's cuBLAS matmul for unquantised weights (/root/reference/src/openai/models/linear.rs:124-172)
+/* ---- dense 16-bit Linear::forward -- replaces candle's cuBLAS matmul for unquantised weights (src/openai/models/linear.rs:124-172)
  * out[m,n] = x[m,k] . weight[n,k]^T (+ bias[n]); x, weight, bias, out of `dtype` (B200_F16 / B200_BF16), contiguous, fp32 accumulation on
  * tcgen05 (128 x 256 tiles for m > 64; swap-AB weight stream for m <= 64).  k % 8 == 0, n % 8 == 0 (16-byte rows). */
 void linear_16bit(const void* x, const void* weight, const void* bias, void* out, int32_t m, int32_t n, int32_t k, int32_t dtype, int64_t stream);
 
 /* ---- K10 / K11 / K12: weight-only low-precision float linears -- replace attention_rs::{fp8_linear::fp8_matmul,
- * nvfp4_linear::nvfp4_matmul, mxfp4_linear::mxfp4_matmul} (call sites /root/reference/src/openai/models/linear.rs:1190-1221,
+ * nvfp4_linear::nvfp4_matmul, mxfp4_linear::mxfp4_matmul} (call sites src/openai/models/linear.rs:1190-1221,
  * :1913-1943, :1717-1757; tensor layouts :944-973, :1812-1853, :1686-1700).
  * out[m,n] = x[m,k] . dequant(W[n,k])^T (+ bias[n]); x, bias, out are f16 or bf16 (`dtype`), fp32 accumulation.
  *   fp8_matmul : weight e4m3 bytes [n,k]; weight_scale f32 [ceil(n/block_y), ceil(k/block_x)] multiplies its tile
@@ -216,7 +216,7 @@ void mxfp4_matmul(const void* x, const void* blocks, const void* scales, const v
                   int32_t k, int32_t dtype, int64_t stream);
 
 /* ---- multi-head latent attention (DeepSeek-V2 / V3) -- replaces attention_rs::mla::{concat_and_cache_mla, mla_paged_decode, mla_paged_prefill}
- * (call sites /root/reference/src/openai/models/layers/mla_attention.rs:479-552; cache shapes /root/reference/src/scheduler/cache_engine.rs:172-185).
+ * (call sites src/openai/models/layers/mla_attention.rs:479-552; cache shapes src/scheduler/cache_engine.rs:172-185).
  *   concat_and_cache_mla: ckv [T, kv_lora_rank], k_pe [T, qk_rope_head_dim] -> ckv_cache [nb, bs, 1, kv_lora_rank], kpe_cache [nb, bs, 1, rope] at
  *     slot_mapping[t] (negative = pad, skipped); 16-bit `dtype`, bit copy.
  *   mla_paged_attention: "absorbed" MLA: q_absorbed [rows, H, kv_lora_rank] (W_uk already folded in), q_pe [rows, H, rope];
@@ -234,7 +234,7 @@ void mla_paged_attention(void* out, const void* q_absorbed, const void* q_pe, co
                          int32_t dtype, void* workspace, size_t workspace_bytes, int64_t stream);
 
 /* ---- fused mixture-of-experts on GGUF expert tensors -- replaces attention_rs::{topk::topk_softmax, moe::moe_gemm_gguf} and the host-side
- * sort (call sites /root/reference/src/openai/models/layers/moe.rs:35-45, :425-480, :1429-1482; quantized_qwen3_moe.rs:70-141).
+ * sort (call sites src/openai/models/layers/moe.rs:35-45, :425-480, :1429-1482; quantized_qwen3_moe.rs:70-141).
  *   topk_softmax: router_logits f32 [T, E] -> topk_weights f32 [T, k] (softmax probabilities of the k largest, NOT renormalised: the
  *     caller applies norm_topk_prob / routed_scaling_factor like the reference), topk_ids u32 [T, k]; ties -> smaller expert id.
  *   sort_expert_assignments: flattened topk_ids u32 [P = T * k] -> expert_ids u32 [P] ascending, sorted_token_ids u32 [P] = the pair index
@@ -253,7 +253,7 @@ void moe_gemm_gguf(const float* x, const void* experts, const float* topk_weight
                    float* out, int32_t num_experts, int32_t topk, int32_t size_m, int32_t num_pairs, int32_t n, int32_t k, int32_t ggml_type,
                    int32_t is_prefill, void* workspace, size_t workspace_bytes, int64_t stream);
 
-/* moe_gemm_fp8 -- replaces attention_rs::moe::moe_gemm_fp8 (call sites /root/reference/src/openai/models/layers/moe.rs:1447-1473, block-FP8
+/* moe_gemm_fp8 -- replaces attention_rs::moe::moe_gemm_fp8 (call sites src/openai/models/layers/moe.rs:1447-1473, block-FP8
  * experts as in DeepSeek-V3 / Qwen3 FP8 checkpoints): x [size_m, k] and out [num_pairs, n] of `dtype` (B200_F16 / B200_BF16); experts e4m3
  * [E, n, k]; scale f32 [E, ceil(n / block_y), ceil(k / block_x)] multiplies the weight tile; routing arguments as moe_gemm_gguf.  Weight-only:
  * activations are rounded to fp16, weights decoded exactly, fp32 accumulation, one rounding to `dtype`.  k % 256 == 0, n % block_y == 0,
@@ -290,7 +290,7 @@ void rope_and_cache(const float* qkv, void* q_out, void* key_cache, void* value_
                     int32_t dtype, int32_t cache_dtype, int64_t stream);
 
 /* ---- decode engine: GGUFLLaMa::forward_inner for one decode step ------------------------------
- * Mirrors /root/reference/src/openai/models/quantized_llama.rs:424-506 (+ attention.rs:910-1011,
+ * Mirrors src/openai/models/quantized_llama.rs:424-506 (+ attention.rs:910-1011,
  * Mlp::forward :32-44) with the reference's CUDA-graph replay protocol (backend/graph.rs:685-803):
  * static device buffers, metadata copied in, one graph launch per step. */
 typedef struct {
@@ -309,7 +309,7 @@ typedef struct {
 } b200_llama_layer;
 
 /* A linear layer of the decode engine.  GGUF models use GGML tensors (b200_llama_layer above is the short form); the safetensors
- * models of the reference use Linear / GPTQ-Marlin / block-FP8 layers (/root/reference/src/openai/models/llama.rs:47-64,
+ * models of the reference use Linear / GPTQ-Marlin / block-FP8 layers (src/openai/models/llama.rs:47-64,
  * linear.rs:124-172, :300-413): BASELINE configs 2 (dense BF16) and 3 (GPTQ/Marlin int4 + FP8 KV). */
 enum { B200_LIN_GGML = 0,      /* w = GGML blocks, type = ggml type */
        B200_LIN_MARLIN4 = 1,   /* w = gptq_repack / awq_repack output, scales = marlin_permute_scales output (type = B200_F16 / B200_BF16 of the
@@ -425,6 +425,9 @@ void embedding_scaled(const void* table, const int32_t* ids, float* out, int32_t
  * gated_delta_rule: qkv f32 [T, G dk | G dk | H dv] (the conv output), b and a = columns off_b + h / off_a + h of `proj` (row pitch ld_proj);
  *   per head, state S f32 stored [slots, H, dv, dk] (a column's rows contiguous): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, q and k unit vectors (eps 1e-6,
  *   q also times dk^-1/2), beta = sigmoid(b), g = exp(-exp(A_log[h]) * softplus(a + dt_bias[h])).  out f32 [T, H dv].  dk <= 256.
+ * gated_delta_rule_tiled: the same rule and arguments, evaluated over tiles of 16 tokens (the state is read and written once per tile, the
+ *   per-tile quantities that do not depend on the value column are prepared for all tiles in parallel); results differ from
+ *   gated_delta_rule by rounding only.  max_rows = the most rows any entry brings; scratch = num_tokens * (2 G dk + 35 H) floats.  dk <= 128.
  * gated_rms_norm: out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[dv] * silu(gate[t, h, :]) (gate row pitch ld_gate). */
 void causal_conv_silu(const float* x, int64_t ldx, const float* taps, float* conv_state, float* y, const int32_t* token_seq,
                       const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens, int32_t num_seqs,
@@ -433,6 +436,10 @@ void gated_delta_rule(const float* qkv, const float* proj, int64_t ld_proj, int3
                       const float* dt_bias, float* state, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots,
                       const int32_t* seq_start, int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv,
                       int64_t stream);
+void gated_delta_rule_tiled(const float* qkv, const float* proj, int64_t ld_proj, int32_t off_b, int32_t off_a, const float* A_log,
+                            const float* dt_bias, float* state, float* out, float* scratch, const int32_t* cu_seqlens,
+                            const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens, int32_t num_seqs, int32_t max_rows,
+                            int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int64_t stream);
 void gated_rms_norm(const float* o, const float* gate, int64_t ld_gate, const float* weight, void* out, int32_t num_tokens, int32_t num_heads,
                     int32_t dv, float eps, int32_t out_dtype, int64_t stream);
 /* qk_norm_rope_cache: qkv f32 [T, H dk | G dk | G dv] (row pitch ld) -> optional RMS norm over the whole q row and the whole k row (weights
@@ -461,7 +468,7 @@ void paged_attention_varlen(void* out, const void* q, const void* key_cache, con
 /* library-wide count of kernels launched by this library (evidence for bench.py's gpu_launches) */
 long long b200_total_kernel_launches(void);
 /* NCCL all-reduce(sum) in place on f32, on the caller's communicator (tensor-parallel residual path,
- * /root/reference/src/openai/distributed.rs:547-654) */
+ * src/openai/distributed.rs:547-654) */
 void b200_allreduce_f32(void* nccl_comm, float* buf, int64_t n, int64_t stream);
 
 #ifdef __cplusplus

@@ -97,10 +97,9 @@ def test_short_convolution_carries_its_inputs(taps, sizes):
     close(torch.cat(got), want, 2e-6, f"taps {taps} portions {sizes}")
 
 
-@pytest.mark.parametrize("H,Gk,dk,dv", [(4, 2, 64, 32), (2, 2, 32, 16), (3, 1, 128, 80), (4, 4, 48, 24), (2, 1, 200, 40)])
-def test_gated_delta_rule(H, Gk, dk, dv):
-    g = torch.Generator().manual_seed(dk + dv)
-    T = 90
+def _delta_case(H, Gk, dk, dv, T, seed):
+    """random inputs of the rule and the plain recurrence over them"""
+    g = torch.Generator().manual_seed(seed)
     Cn = 2 * Gk * dk + H * dv
     qkv = torch.randn(T, Cn, generator=g)
     proj = torch.randn(T, 2 * H + 3, generator=g) * 2
@@ -113,13 +112,59 @@ def test_gated_delta_rule(H, Gk, dk, dv):
     beta = torch.sigmoid(proj[:, 1:1 + H].to(F64))
     decay = torch.exp(-torch.exp(A_log.to(F64)) * torch.nn.functional.softplus(proj[:, 2 + H:2 + 2 * H].to(F64) + dt_bias.to(F64)))
     want = G.delta_recurrence(q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1), v, beta, decay).reshape(T, H * dv)
-    for sizes in ([T], [1], [2, 3, 1, 17]):
+    return qkv, proj, A_log, dt_bias, want
+
+
+@pytest.mark.parametrize("tiled", [False, True])
+@pytest.mark.parametrize("H,Gk,dk,dv", [(4, 2, 64, 32), (2, 2, 32, 16), (3, 1, 128, 80), (4, 4, 48, 24), (2, 1, 200, 40), (2, 1, 30, 17)])
+def test_gated_delta_rule(H, Gk, dk, dv, tiled):
+    """both kernels of the rule (token by token; over tiles of 16 tokens), alone"""
+    if tiled and dk > 128:
+        pytest.skip("the tiled kernel takes key sizes up to 128")
+    T = 90
+    qkv, proj, A_log, dt_bias, want = _delta_case(H, Gk, dk, dv, T, dk + dv)
+    for sizes in ([T], [1], [2, 3, 1, 17], [16], [33, 15, 32, 7]):
         state = torch.full((2, H, dv, dk), 3.0, device=DEV)
         got = []
         for at, n in _portions(T, sizes):
             b = batch_of([dict(tokens=[0] * n, start=at, block_table=[0, 1], state_slot=1, want=[])])
-            got.append(ops.gated_delta_rule(dev(qkv)[at:at + n], dev(proj)[at:at + n], 1, 2 + H, dev(A_log), dev(dt_bias), state, b, H, Gk, dk, dv))
+            got.append(ops.gated_delta_rule(dev(qkv)[at:at + n], dev(proj)[at:at + n], 1, 2 + H, dev(A_log), dev(dt_bias), state, b, H, Gk, dk, dv, tiled=tiled))
         close(torch.cat(got), want, 5e-6, f"portions {sizes}")
+
+
+@pytest.mark.parametrize("tiled", [False, True, None])
+def test_gated_delta_rule_unequal_entries(tiled):
+    """Several sequences in one step, portions of unequal length beside single tokens, each continuing from its own slot: every one
+    comes out as it does alone.  The two kernels hand the state to each other between steps."""
+    H, Gk, dk, dv = 4, 2, 40, 24
+    lens = [37, 1, 16, 5, 70]
+    cases = [_delta_case(H, Gk, dk, dv, n + 9, 100 + i) for i, n in enumerate(lens)]
+    state = torch.full((len(lens) + 1, H, dv, dk), -2.0, device=DEV)
+    A_log, dt_bias = cases[0][2], cases[0][3]                # one model: the same per-head constants for every sequence
+    outs = [[] for _ in lens]
+    for step, take in enumerate((lambda n: n, lambda n: 1, lambda n: 8)):
+        rows_q, rows_p, entries, spans = [], [], [], []
+        for i, n in enumerate(lens):
+            at = 0 if step == 0 else (n if step == 1 else n + 1)
+            m = take(n)
+            rows_q.append(cases[i][0][at:at + m]); rows_p.append(cases[i][1][at:at + m])
+            entries.append(dict(tokens=[0] * m, start=at, block_table=[0, 1], state_slot=len(lens) - i, want=[]))
+            spans.append(m)
+        b = batch_of(entries)
+        got = ops.gated_delta_rule(dev(torch.cat(rows_q)), dev(torch.cat(rows_p)), 1, 2 + H, dev(A_log), dev(dt_bias), state, b, H, Gk, dk, dv,
+                                   tiled=tiled)
+        for i, piece in enumerate(torch.split(got, spans)):
+            outs[i].append(piece)
+    for i, n in enumerate(lens):
+        qkv, proj, _, _, _ = cases[i]
+        # the oracle with this test's shared constants
+        q = G.unit(qkv[:, :Gk * dk].to(F64).view(-1, Gk, dk)) * dk ** -0.5
+        k = G.unit(qkv[:, Gk * dk:2 * Gk * dk].to(F64).view(-1, Gk, dk))
+        v = qkv[:, 2 * Gk * dk:].to(F64).view(-1, H, dv)
+        beta = torch.sigmoid(proj[:, 1:1 + H].to(F64))
+        decay = torch.exp(-torch.exp(A_log.to(F64)) * torch.nn.functional.softplus(proj[:, 2 + H:2 + 2 * H].to(F64) + dt_bias.to(F64)))
+        ref = G.delta_recurrence(q.repeat_interleave(H // Gk, 1), k.repeat_interleave(H // Gk, 1), v, beta, decay).reshape(-1, H * dv)
+        close(torch.cat(outs[i]), ref, 5e-6, f"entry {i} ({n} rows, then 1, then 8)")
 
 
 def test_gated_rms_norm():
