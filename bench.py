@@ -816,6 +816,13 @@ def run_gobesun(args):
                 if w:
                     roof = w[1] / (HBM if w[0] == "bytes" else TC)
                     e.update(bound=w[0], roofline_us=round(roof * 1e6, 2), frac_of_measured_peak=round(roof / t, 3))
+                if key == "gated_delta_rule" and tag == "prefill":
+                    # the recurrence is 32-bit by definition, so its arithmetic runs on the FMA pipe, not on tensor cores: three
+                    # multiply-adds per state element per token against the nominal f32 rate (SMs x 128 lanes x 2 x max clock)
+                    props = torch.cuda.get_device_properties(0)
+                    f32_peak = props.multi_processor_count * 128 * 2 * 1.965e9
+                    roof32 = 6.0 * T * H * hd * hd / f32_peak
+                    e.update(f32_fma_roofline_us=round(roof32 * 1e6, 2), frac_of_nominal_f32_fma=round(roof32 / t, 3))
                 out[key] = e
             return out
         results[name] = {
