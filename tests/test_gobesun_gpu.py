@@ -116,7 +116,7 @@ def _delta_case(H, Gk, dk, dv, T, seed):
 
 
 @pytest.mark.parametrize("tiled", [False, True])
-@pytest.mark.parametrize("H,Gk,dk,dv", [(4, 2, 64, 32), (2, 2, 32, 16), (3, 1, 128, 80), (4, 4, 48, 24), (2, 1, 200, 40), (2, 1, 30, 17)])
+@pytest.mark.parametrize("H,Gk,dk,dv", [(4, 2, 64, 32), (2, 2, 32, 16), (3, 1, 128, 80), (4, 4, 48, 24), (2, 1, 200, 40), (2, 1, 30, 17), (2, 2, 300, 20)])
 def test_gated_delta_rule(H, Gk, dk, dv, tiled):
     """both kernels of the rule (token by token; over tiles of 16 tokens), alone"""
     if tiled and dk > 128:
