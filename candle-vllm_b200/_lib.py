@@ -34,7 +34,7 @@ SYMBOLS = [
     "b200_total_kernel_launches", "b200_allreduce_f32",
     "gptq_repack", "marlin_checkpoint_repack", "awq_repack", "marlin_4bit_f16", "marlin_4bit_bf16", "marlin_awq_4bit_f16", "marlin_awq_4bit_bf16",
     "gemm_half_q_half_alt", "b200_set_scratch",
-    "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled", "causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_rms_norm",
+    "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled", "causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_delta_rule_step", "gated_rms_norm",
     "qk_norm_rope_cache", "paged_attention_varlen", "chunk_decode_view",
 ]
 
@@ -43,7 +43,7 @@ SYMBOLS = [
 GROUP_SYMBOLS = {
     "ragged": ["b200_abi_version", "b200_last_error", "b200_last_error_message", "b200_device_sm_count", "b200_device_cc",
                "b200_total_kernel_launches", "linear_16bit", "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled",
-               "causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_rms_norm", "qk_norm_rope_cache", "paged_attention_varlen", "chunk_decode_view",
+               "causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_delta_rule_step", "gated_rms_norm", "qk_norm_rope_cache", "paged_attention_varlen", "chunk_decode_view",
                "paged_attention_decode", "paged_attention_decode_workspace_bytes", "argmax_f32",
                "rms_norm", "cast"],
 }

@@ -226,6 +226,103 @@ gated_delta_rule_kernel(const float* __restrict__ qkv, const float* __restrict__
     }
 }
 
+// ---- steps of single tokens ------------------------------------------------------------------------------------------------------
+// Every entry brings one token: the work is one read and one write of the state.  Same lane layout as above (4 columns x 8 parts of kR
+// rows per warp, 16 columns per block), but nothing is staged: a lane's state loads go out first, every warp works out the token's unit
+// norms, k . q, beta and decay for itself (the q / k rows are a few hundred bytes and stay in L1), and a lane reads its own kR entries
+// of q and k straight from the rows.  No shared memory, no block-wide barrier, ~80 registers: six and more blocks per SM keep the state
+// traffic in flight.  The sums are those of gated_delta_rule_kernel in the same order.
+template <int kR>
+__global__ void __launch_bounds__(128)
+gated_delta_step_kernel(const float* __restrict__ qkv, const float* __restrict__ proj, int64_t ld_proj, int off_b, int off_a,
+                        const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ state, float* __restrict__ out,
+                        const int32_t* __restrict__ seq_slots, const int32_t* __restrict__ seq_start, int H, int G, int dk, int dv) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int kDP = 8 * kR;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, part = lane >> 2;
+    const int t = blockIdx.z, h = blockIdx.y;          // entry = row
+    const int col = blockIdx.x * 16 + warp * 4 + (lane & 3);
+    const bool live = col < dv;
+    const int g = h / (H / G);
+    const int C = 2 * G * dk + H * dv;
+    const int row0 = part * kR;
+    float* Sg = state + (((int64_t)seq_slots[t] * H + h) * dv + (live ? col : 0)) * dk + row0;
+    const bool fresh = seq_start[t] == 0;
+    const bool vec = (dk & 3) == 0 && row0 + kR <= dk;
+    float S[kR];
+    if (live && !fresh && vec) {
+#pragma unroll
+        for (int r = 0; r < kR; r += 4) {
+            const float4 t4 = *reinterpret_cast<const float4*>(Sg + r);
+            S[r] = t4.x; S[r + 1] = t4.y; S[r + 2] = t4.z; S[r + 3] = t4.w;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < kR; ++r) S[r] = (live && !fresh && row0 + r < dk) ? Sg[r] : 0.f;
+    }
+    const float* qrow = qkv + (int64_t)t * C + g * dk;
+    const float* krow = qrow + G * dk;
+    float kd[kR], qd[kR];
+    if (vec && (C & 3) == 0) {
+#pragma unroll
+        for (int r = 0; r < kR; r += 4) {
+            const float4 c = *reinterpret_cast<const float4*>(krow + row0 + r), a = *reinterpret_cast<const float4*>(qrow + row0 + r);
+            kd[r] = c.x; kd[r + 1] = c.y; kd[r + 2] = c.z; kd[r + 3] = c.w;
+            qd[r] = a.x; qd[r + 1] = a.y; qd[r + 2] = a.z; qd[r + 3] = a.w;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < kR; ++r) {
+            const bool in = row0 + r < dk;
+            kd[r] = in ? krow[row0 + r] : 0.f;
+            qd[r] = in ? qrow[row0 + r] : 0.f;
+        }
+    }
+    const float v = live ? qkv[(int64_t)t * C + 2 * G * dk + h * dv + col] : 0.f;
+    float qq = 0.f, kk = 0.f, qk = 0.f;
+    for (int i = lane; i < kDP; i += 32) {
+        const float a = i < dk ? qrow[i] : 0.f, c = i < dk ? krow[i] : 0.f;
+        qq = fmaf(a, a, qq); kk = fmaf(c, c, kk); qk = fmaf(a, c, qk);
+    }
+    qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
+    const float qn = (1.0f / sqrtf((float)dk)) / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
+    const float kq = qk * qn * kn;
+    const float beta = 1.0f / (1.0f + expf(-proj[(int64_t)t * ld_proj + off_b + h]));
+    const float decay = expf(-expf(A_log[h]) * softplus_f(proj[(int64_t)t * ld_proj + off_a + h] + dt_bias[h]));
+    float p[4] = {0.f, 0.f, 0.f, 0.f}, o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kR; r += 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            kd[r + j] *= kn; qd[r + j] *= qn;
+            p[j] = fmaf(S[r + j], kd[r + j], p[j]);
+            o[j] = fmaf(S[r + j], qd[r + j], o[j]);
+        }
+    }
+    float pk = (p[0] + p[1]) + (p[2] + p[3]), pq = (o[0] + o[1]) + (o[2] + o[3]);
+#pragma unroll
+    for (int m = 4; m <= 16; m <<= 1) {
+        const float x = __shfl_xor_sync(0xffffffffu, pk, m), y = __shfl_xor_sync(0xffffffffu, pq, m);
+        pk += x; pq += y;
+    }
+    const float u = beta * (v - decay * pk);
+    const float ov = fmaf(u, kq, decay * pq);
+#pragma unroll
+    for (int r = 0; r < kR; ++r) S[r] = fmaf(kd[r], u, decay * S[r]);
+    if (live) {
+        if (part == 0) out[(int64_t)t * H * dv + h * dv + col] = ov;
+        if (vec) {
+#pragma unroll
+            for (int r = 0; r < kR; r += 4) *reinterpret_cast<float4*>(Sg + r) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
+        } else {
+#pragma unroll
+            for (int r = 0; r < kR; ++r)
+                if (row0 + r < dk) Sg[r] = S[r];
+        }
+    }
+}
+
 // ---- the rule over tiles of 16 tokens -------------------------------------------------------------------------------------------
 // Inside a tile that starts from state S0, with decays g_i, P_i = g_0 ... g_i and R_is = g_{s+1} ... g_i:
 //     S_i = P_i S0 + sum_{s<=i} R_is k_s u_s^T
@@ -609,6 +706,28 @@ void gated_delta_rule(const float* qkv, const float* proj, int64_t ld_proj, int3
 #undef GDR
     count_launch();
     check_launch("gated_delta_rule");
+}
+
+void gated_delta_rule_step(const float* qkv, const float* proj, int64_t ld_proj, int32_t off_b, int32_t off_a, const float* A_log, const float* dt_bias,
+                           float* state, float* out, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs, int32_t num_heads,
+                           int32_t num_kv_heads, int32_t dk, int32_t dv, int64_t stream) {
+    if (num_seqs == 0) return;
+    B200_REQUIRE(qkv && proj && A_log && dt_bias && state && out && seq_slots && seq_start, kErrBadArg, "gated_delta_rule_step: null pointer");
+    B200_REQUIRE(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dk > 0 && dv > 0 && num_seqs <= 65535, kErrBadArg,
+                 "gated_delta_rule_step: bad sizes");
+    B200_REQUIRE(dk <= 512, kErrUnsupported, "gated_delta_rule_step: key size %d > 512", dk);
+    cudaStream_t st = as_stream(stream);
+    const dim3 grid(ceil_div(dv, 16), num_heads, num_seqs);
+#define GDS(R) launch_pdl(gated_delta_step_kernel<R>, grid, dim3(128), 0, st, qkv, proj, ld_proj, off_b, off_a, A_log, dt_bias, state, out, seq_slots, seq_start, \
+                          num_heads, num_kv_heads, dk, dv)
+    if (dk <= 32) GDS(4);
+    else if (dk <= 64) GDS(8);
+    else if (dk <= 128) GDS(16);
+    else if (dk <= 256) GDS(32);
+    else GDS(64);
+#undef GDS
+    count_launch();
+    check_launch("gated_delta_rule_step");
 }
 
 void gated_delta_rule_tiled(const float* qkv, const float* proj, int64_t ld_proj, int32_t off_b, int32_t off_a, const float* A_log, const float* dt_bias,

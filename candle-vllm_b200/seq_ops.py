@@ -126,27 +126,37 @@ TILED_DELTA_MIN_ROWS = 8      # steps in which some entry brings at least this m
 
 
 def gated_delta_rule(qkv: torch.Tensor, proj: torch.Tensor, off_b: int, off_a: int, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
-                     batch: StepBatch, heads: int, kv_heads: int, dk: int, dv: int, tiled: Optional[bool] = None) -> torch.Tensor:
+                     batch: StepBatch, heads: int, kv_heads: int, dk: int, dv: int, kernel: Optional[str] = None) -> torch.Tensor:
     """qkv f32 [T, G dk | G dk | H dv]; b / a read from columns off_b.. / off_a.. of ``proj``; state f32 [slots, H, dv, dk] advanced in place.
-    Two kernels compute the same rule: token by token (single decoded tokens, short portions), and over tiles of 16 tokens (portions of
-    prompts; key sizes up to 128).  ``tiled`` forces one of them; None chooses by the longest portion of the step."""
+    Three kernels compute the same rule: "step" (every entry brings one token: one pass over the state, nothing staged), "tiled" (over
+    tiles of 16 tokens, for portions of prompts; key sizes up to 128) and "token" (token by token, any step).  ``kernel`` forces one;
+    None chooses by the step's shape."""
     T = qkv.shape[0]
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=qkv.device)
     ld_proj = C.c_int64(proj.stride(0) if T > 1 else proj.shape[1])
-    if tiled is None:
-        tiled = dk <= 128 and batch.max_rows >= TILED_DELTA_MIN_ROWS
-    if tiled:
+    if kernel is None:
+        kernel = "step" if batch.pure_decode else "tiled" if (dk <= 128 and batch.max_rows >= TILED_DELTA_MIN_ROWS) else "token"
+    if kernel == "step":
+        if T != batch.num_seqs:
+            raise BackendError("gated_delta_rule: the single-token kernel takes one row per entry")
+        lib().gated_delta_rule_step(_ptr(qkv), _ptr(proj), ld_proj, C.c_int32(off_b), C.c_int32(off_a), _ptr(A_log), _ptr(dt_bias), _ptr(state), _ptr(out),
+                                    _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(batch.num_seqs), C.c_int32(heads), C.c_int32(kv_heads),
+                                    C.c_int32(dk), C.c_int32(dv), _stream(qkv.device))
+        check("gated_delta_rule_step")
+    elif kernel == "tiled":
         scratch = torch.empty((T * (2 * kv_heads * dk + 35 * heads),), dtype=torch.float32, device=qkv.device)
         lib().gated_delta_rule_tiled(_ptr(qkv), _ptr(proj), ld_proj, C.c_int32(off_b), C.c_int32(off_a), _ptr(A_log), _ptr(dt_bias), _ptr(state), _ptr(out),
                                      _ptr(scratch), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(T),
                                      C.c_int32(batch.num_seqs), C.c_int32(batch.max_rows), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk),
                                      C.c_int32(dv), _stream(qkv.device))
         check("gated_delta_rule_tiled")
-        return out
-    lib().gated_delta_rule(_ptr(qkv), _ptr(proj), ld_proj, C.c_int32(off_b), C.c_int32(off_a), _ptr(A_log),
-                           _ptr(dt_bias), _ptr(state), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start),
-                           C.c_int32(batch.num_seqs), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk), C.c_int32(dv), _stream(qkv.device))
-    check("gated_delta_rule")
+    elif kernel == "token":
+        lib().gated_delta_rule(_ptr(qkv), _ptr(proj), ld_proj, C.c_int32(off_b), C.c_int32(off_a), _ptr(A_log),
+                               _ptr(dt_bias), _ptr(state), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start),
+                               C.c_int32(batch.num_seqs), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk), C.c_int32(dv), _stream(qkv.device))
+        check("gated_delta_rule")
+    else:
+        raise BackendError(f"gated_delta_rule: unknown kernel {kernel!r}")
     return out
 
 

@@ -425,6 +425,8 @@ void embedding_scaled(const void* table, const int32_t* ids, float* out, int32_t
  * gated_delta_rule: qkv f32 [T, G dk | G dk | H dv] (the conv output), b and a = columns off_b + h / off_a + h of `proj` (row pitch ld_proj);
  *   per head, state S f32 stored [slots, H, dv, dk] (a column's rows contiguous): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, q and k unit vectors (eps 1e-6,
  *   q also times dk^-1/2), beta = sigmoid(b), g = exp(-exp(A_log[h]) * softplus(a + dt_bias[h])).  out f32 [T, H dv].  dk <= 512.
+ * gated_delta_rule_step: the same rule for steps in which every entry brings exactly one row (row t belongs to entry t): one read and one
+ *   write of the state, nothing staged.
  * gated_delta_rule_tiled: the same rule and arguments, evaluated over tiles of 16 tokens (the state is read and written once per tile, the
  *   per-tile quantities that do not depend on the value column are prepared for all tiles in parallel); results differ from
  *   gated_delta_rule by rounding only.  max_rows = the most rows any entry brings; scratch = num_tokens * (2 G dk + 35 H) floats.  dk <= 128.
@@ -436,6 +438,9 @@ void gated_delta_rule(const float* qkv, const float* proj, int64_t ld_proj, int3
                       const float* dt_bias, float* state, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots,
                       const int32_t* seq_start, int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv,
                       int64_t stream);
+void gated_delta_rule_step(const float* qkv, const float* proj, int64_t ld_proj, int32_t off_b, int32_t off_a, const float* A_log,
+                           const float* dt_bias, float* state, float* out, const int32_t* seq_slots, const int32_t* seq_start,
+                           int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int64_t stream);
 void gated_delta_rule_tiled(const float* qkv, const float* proj, int64_t ld_proj, int32_t off_b, int32_t off_a, const float* A_log,
                             const float* dt_bias, float* state, float* out, float* scratch, const int32_t* cu_seqlens,
                             const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens, int32_t num_seqs, int32_t max_rows,

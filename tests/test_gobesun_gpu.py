@@ -115,27 +115,27 @@ def _delta_case(H, Gk, dk, dv, T, seed):
     return qkv, proj, A_log, dt_bias, want
 
 
-@pytest.mark.parametrize("tiled", [False, True])
+@pytest.mark.parametrize("kernel", ["token", "tiled", "step"])
 @pytest.mark.parametrize("H,Gk,dk,dv", [(4, 2, 64, 32), (2, 2, 32, 16), (3, 1, 128, 80), (4, 4, 48, 24), (2, 1, 200, 40), (2, 1, 30, 17), (2, 2, 300, 20)])
-def test_gated_delta_rule(H, Gk, dk, dv, tiled):
-    """both kernels of the rule (token by token; over tiles of 16 tokens), alone"""
-    if tiled and dk > 128:
+def test_gated_delta_rule(H, Gk, dk, dv, kernel):
+    """the kernels of the rule, alone: token by token; over tiles of 16 tokens; one token per entry (portions of one row only)"""
+    if kernel == "tiled" and dk > 128:
         pytest.skip("the tiled kernel takes key sizes up to 128")
-    T = 90
+    T = 90 if kernel != "step" else 40
     qkv, proj, A_log, dt_bias, want = _delta_case(H, Gk, dk, dv, T, dk + dv)
-    for sizes in ([T], [1], [2, 3, 1, 17], [16], [33, 15, 32, 7]):
+    for sizes in ([T], [1], [2, 3, 1, 17], [16], [33, 15, 32, 7]) if kernel != "step" else ([1],):
         state = torch.full((2, H, dv, dk), 3.0, device=DEV)
         got = []
         for at, n in _portions(T, sizes):
             b = batch_of([dict(tokens=[0] * n, start=at, block_table=[0, 1], state_slot=1, want=[])])
-            got.append(ops.gated_delta_rule(dev(qkv)[at:at + n], dev(proj)[at:at + n], 1, 2 + H, dev(A_log), dev(dt_bias), state, b, H, Gk, dk, dv, tiled=tiled))
-        close(torch.cat(got), want, 5e-6, f"portions {sizes}")
+            got.append(ops.gated_delta_rule(dev(qkv)[at:at + n], dev(proj)[at:at + n], 1, 2 + H, dev(A_log), dev(dt_bias), state, b, H, Gk, dk, dv, kernel=kernel))
+        close(torch.cat(got), want[:T], 5e-6, f"portions {sizes}")
 
 
-@pytest.mark.parametrize("tiled", [False, True, None])
-def test_gated_delta_rule_unequal_entries(tiled):
+@pytest.mark.parametrize("kernel", ["token", "tiled", None])
+def test_gated_delta_rule_unequal_entries(kernel):
     """Several sequences in one step, portions of unequal length beside single tokens, each continuing from its own slot: every one
-    comes out as it does alone.  The two kernels hand the state to each other between steps."""
+    comes out as it does alone.  With kernel = None the tiled, the single-token and again the tiled kernel run in turn and hand the state on."""
     H, Gk, dk, dv = 4, 2, 40, 24
     lens = [37, 1, 16, 5, 70]
     cases = [_delta_case(H, Gk, dk, dv, n + 9, 100 + i) for i, n in enumerate(lens)]
@@ -152,7 +152,7 @@ def test_gated_delta_rule_unequal_entries(tiled):
             spans.append(m)
         b = batch_of(entries)
         got = ops.gated_delta_rule(dev(torch.cat(rows_q)), dev(torch.cat(rows_p)), 1, 2 + H, dev(A_log), dev(dt_bias), state, b, H, Gk, dk, dv,
-                                   tiled=tiled)
+                                   kernel=kernel)
         for i, piece in enumerate(torch.split(got, spans)):
             outs[i].append(piece)
     for i, n in enumerate(lens):
