@@ -33,9 +33,9 @@ def _newer(target: str, deps) -> bool:
 
 # Source groups that link into a library of their own: what one model family needs, so that a first start from a source-only checkout
 # compiles that and nothing else.  "ragged" = the ragged-step decoders (seq_ops.py): error state, both linear kernels, norms /
-# activations, recurrent and attention mixers, argmax.
+# activations, recurrent, attention and latent-attention mixers, routed experts, argmax.
 GROUPS = {"ragged": ["lib", "linear_generic", "dense_gemm", "norm_act", "gated_delta", "attention_varlen", "attention_prefill", "attention_decode", "attention_generic",
-                     "attention_api", "elementwise"]}
+                     "attention_api", "elementwise", "latent_attention", "moe_ragged"]}
 
 
 def so_path(group=None) -> str:

@@ -1,0 +1,195 @@
+// moe_ragged.cu -- mixture of experts on dense f32 / bf16 expert weights for ragged steps: the router's choice and the expert
+// feed-forward for steps of few rows (every (token, choice) pair streams its expert once; steps with many rows sort the pairs by
+// expert and run the expert products on the tensor-core GEMM instead).
+//
+//   moe_route         per token, from f32 router logits z [N]: s = softmax(z) over all N outputs; choice score = s + correction; the
+//                     outputs form `groups` equal runs of neighbours, a group's score is its best choice score, and only members of the
+//                     `keep` best groups can be chosen (the others count as -inf); the `top` best choice scores are taken (ties: the lower
+//                     index); weights = s of the chosen / (their sum + 1e-20) * scale.  groups <= 1 switches the restriction off.
+//   moe_gate_up       act[p] = silu(W_gate[e] h) * (W_up[e] h) for pair p = (token, choice) with expert e < E; outputs e >= E are identity
+//                     experts (no weights) and are skipped.
+//   moe_down_combine  out[t] = sum over the token's choices, in choice order, of weight * (W_down[e] act[p]), or weight * x[t] for an
+//                     identity expert.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+__global__ void __launch_bounds__(32)
+moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ correction, int32_t* __restrict__ ids, float* __restrict__ weights,
+                 int N, int top, int groups, int keep, float scale) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float sm[];
+    float* s = sm;                 // [N] softmax
+    float* pick = sm + N;          // [N] choice scores, -inf once masked or taken
+    float* gbest = sm + 2 * N;     // [groups]
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const float* z = logits + (int64_t)t * ld;
+    float mx = -INFINITY;
+    for (int i = lane; i < N; i += 32) mx = fmaxf(mx, z[i]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int i = lane; i < N; i += 32) { const float e = expf(z[i] - mx); s[i] = e; sum += e; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int i = lane; i < N; i += 32) { s[i] *= inv; pick[i] = s[i] + (correction ? correction[i] : 0.f); }
+    __syncwarp();
+    if (groups > 1) {
+        const int per = N / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float b = -INFINITY;
+            for (int i = 0; i < per; ++i) b = fmaxf(b, pick[g * per + i]);
+            gbest[g] = b;
+        }
+        __syncwarp();
+        // take the `keep` best groups one at a time; a taken group is marked +inf, the rest are masked afterwards
+        for (int r = 0; r < keep; ++r) {
+            float b = -INFINITY; int bi = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) { const float v = gbest[g]; if (v != INFINITY && (v > b || bi == 0x7fffffff)) { b = v; bi = g; } }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, b, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > b || (ob == b && oi < bi))) { b = ob; bi = oi; }
+            }
+            if (lane == 0 && bi != 0x7fffffff) gbest[bi] = INFINITY;
+            __syncwarp();
+        }
+        for (int i = lane; i < N; i += 32) if (gbest[i / per] != INFINITY) pick[i] = -INFINITY;
+        __syncwarp();
+    }
+    float wsum = 0.f;
+    for (int r = 0; r < top; ++r) {
+        float b = -INFINITY; int bi = 0x7fffffff;
+        for (int i = lane; i < N; i += 32) { const float v = pick[i]; if (!isnan(v) && (bi == 0x7fffffff ? v > -INFINITY : v > b)) { b = v; bi = i; } }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, b, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > b || (ob == b && oi < bi))) { b = ob; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;                      // fewer eligible outputs than `top` (a configuration error): repeat output 0 with weight s[0]
+        if (lane == 0) { ids[(int64_t)t * top + r] = bi; pick[bi] = NAN; }
+        wsum += s[bi];
+        __syncwarp();
+    }
+    const float norm = scale / (wsum + 1e-20f);
+    for (int r = lane; r < top; r += 32) weights[(int64_t)t * top + r] = s[ids[(int64_t)t * top + r]] * norm;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gate_up_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ w_gu, const int32_t* __restrict__ ids, T* __restrict__ act, int top, int E,
+                   int ff, int D) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float hs[];                          // [D]
+    const int64_t p = blockIdx.x;
+    const int e = ids[p];
+    if (e < 0 || e >= E) return;                           // identity expert: nothing to compute
+    const int64_t t = p / top;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < D; i += 128) hs[i] = to_f32<T>(h[t * ldh + i]);
+    __syncthreads();
+    const T* wg = w_gu + (int64_t)e * 2 * ff * D;           // [gate rows | up rows][D]
+    for (int j = warp; j < ff; j += 4) {
+        const T* g = wg + (int64_t)j * D;
+        const T* u = wg + (int64_t)(ff + j) * D;
+        float a = 0.f, b = 0.f;
+        for (int i = lane; i < D; i += 32) { const float x = hs[i]; a = fmaf(x, to_f32<T>(g[i]), a); b = fmaf(x, to_f32<T>(u[i]), b); }
+        a = warp_sum(a); b = warp_sum(b);
+        if (lane == 0) act[p * ff + j] = from_f32<T>(a / (1.0f + expf(-a)) * b);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_down_combine_kernel(const T* __restrict__ act, const T* __restrict__ w_d, const int32_t* __restrict__ ids, const float* __restrict__ weights,
+                        const float* __restrict__ x, int64_t ldx, float* __restrict__ out, int top, int E, int ff, int D) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float as[];                          // [top][ff]
+    const int64_t t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int k = 0; k < top; ++k) {
+        const int e = ids[t * top + k];
+        if (e >= 0 && e < E)
+            for (int i = threadIdx.x; i < ff; i += 256) as[k * ff + i] = to_f32<T>(act[(t * top + k) * ff + i]);
+    }
+    __syncthreads();
+    for (int d = warp; d < D; d += 8) {
+        float tot = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int e = ids[t * top + k];
+            const float wk = weights[t * top + k];
+            if (e >= 0 && e < E) {
+                const T* w = w_d + ((int64_t)e * D + d) * ff;
+                float a = 0.f;
+                for (int i = lane; i < ff; i += 32) a = fmaf(as[k * ff + i], to_f32<T>(w[i]), a);
+                tot = fmaf(wk, warp_sum(a), tot);
+            } else {
+                tot = fmaf(wk, x[t * ldx + d], tot);
+            }
+        }
+        if (lane == 0) out[t * D + d] = tot;
+    }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+void moe_route(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* weights, int32_t num_tokens, int32_t num_outputs, int32_t top,
+               int32_t groups, int32_t keep, float scale, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(logits && ids && weights && num_outputs > 0 && top > 0 && top <= num_outputs && ld >= num_outputs, kErrBadArg, "moe_route: bad arguments");
+    B200_REQUIRE(groups <= 1 || (num_outputs % groups == 0 && keep > 0 && keep <= groups), kErrBadArg, "moe_route: %d outputs do not form %d equal groups (keep %d)",
+                 num_outputs, groups, keep);
+    B200_REQUIRE(num_outputs <= 8192, kErrUnsupported, "moe_route: more than 8192 router outputs");
+    const size_t smem = ((size_t)2 * num_outputs + (groups > 1 ? groups : 1)) * sizeof(float);
+    launch_pdl(moe_route_kernel, dim3(num_tokens), dim3(32), smem, as_stream(stream), logits, ld, correction, ids, weights, num_outputs, top, groups, keep, scale);
+    count_launch();
+    check_launch("moe_route");
+}
+
+void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, void* act, int32_t num_tokens, int32_t top, int32_t num_experts,
+                 int32_t ff, int32_t width, int32_t dtype, int64_t stream) {
+    if (num_tokens == 0 || num_experts == 0) return;
+    B200_REQUIRE(h && w_gate_up && ids && act && top > 0 && ff > 0 && width > 0 && width <= 16384 && ldh >= width, kErrBadArg, "moe_gate_up: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    const dim3 grid((unsigned)((int64_t)num_tokens * top));
+    const size_t smem = (size_t)width * sizeof(float);
+    ensure_dynamic_smem(reinterpret_cast<const void*>(moe_gate_up_kernel<float>), (int)smem);
+    ensure_dynamic_smem(reinterpret_cast<const void*>(moe_gate_up_kernel<__nv_bfloat16>), (int)smem);
+    if (dtype == B200_F32)
+        launch_pdl(moe_gate_up_kernel<float>, grid, dim3(128), smem, st, (const float*)h, ldh, (const float*)w_gate_up, ids, (float*)act, top, num_experts, ff, width);
+    else if (dtype == B200_BF16)
+        launch_pdl(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(128), smem, st, (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w_gate_up, ids,
+                   (__nv_bfloat16*)act, top, num_experts, ff, width);
+    else { set_error(kErrUnsupported, "moe_gate_up: dtype %d (f32 / bf16)", dtype); return; }
+    count_launch();
+    check_launch("moe_gate_up");
+}
+
+void moe_down_combine(const void* act, const void* w_down, const int32_t* ids, const float* weights, const float* x, int64_t ldx, float* out,
+                      int32_t num_tokens, int32_t top, int32_t num_experts, int32_t ff, int32_t width, int32_t dtype, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(ids && weights && x && out && top > 0 && width > 0 && ldx >= width && (num_experts == 0 || (act && w_down && ff > 0)), kErrBadArg,
+                 "moe_down_combine: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    const size_t smem = (size_t)top * (ff > 0 ? ff : 1) * sizeof(float);
+    B200_REQUIRE(smem <= 160 * 1024, kErrUnsupported, "moe_down_combine: top * ff = %d floats do not fit shared memory", top * ff);
+    if (dtype == B200_F32) {
+        ensure_dynamic_smem(reinterpret_cast<const void*>(moe_down_combine_kernel<float>), (int)smem);
+        launch_pdl(moe_down_combine_kernel<float>, dim3(num_tokens), dim3(256), smem, st, (const float*)act, (const float*)w_down, ids, weights, x, ldx, out, top,
+                   num_experts, ff, width);
+    } else if (dtype == B200_BF16) {
+        ensure_dynamic_smem(reinterpret_cast<const void*>(moe_down_combine_kernel<__nv_bfloat16>), (int)smem);
+        launch_pdl(moe_down_combine_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(256), smem, st, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, ids,
+                   weights, x, ldx, out, top, num_experts, ff, width);
+    } else { set_error(kErrUnsupported, "moe_down_combine: dtype %d (f32 / bf16)", dtype); return; }
+    count_launch();
+    check_launch("moe_down_combine");
+}
+
+}  // extern "C"

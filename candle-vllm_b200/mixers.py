@@ -6,6 +6,11 @@ kernels of ``seq_ops``.  Sizes and constants are constructor arguments so that a
   PagedAttentionMixer  grouped-query attention over the paged cache with optional whole-row q / k RMS norm, partial rotary with
                        optional YaRN scaling, and a chunk and / or sliding-window mask (csrc/attention_varlen.cu)
   GatedMlp             down(act(gate x) * (up x)) with the tanh GELU (csrc/norm_act.cu)
+  LatentAttentionMixer attention over a cached low-rank latent plus one shared rotated key part, softmax sink, sigmoid head gates, optionally
+                       over another layer's cache (csrc/latent_attention.cu)
+  RoutedExperts        softmax-routed mixture of SiLU experts: group-limited top-k with a choice-only correction, identity experts
+                       (csrc/moe_ragged.cu)
+  TokenSideInput       a per-token embedding gated by the stream and added back through a norm
 
 Activations that feed a matrix product are of the model's compute dtype (bf16 or f32); products come back in f32 and everything
 between them (norms, convolution, recurrence, softmax) is 32-bit.
@@ -135,3 +140,110 @@ class GatedMlp:
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return ops.linear(ops.gelu_tanh_mul(ops.linear(h, self.w_in), self.dtype), self.w_down)
+
+
+class LatentAttentionMixer:
+    """Multi-head attention over a low-rank latent: per token the cache holds the normed latent c [rank] and one rotated key part [rot_dim] shared by
+    all heads; head h's key is (W_uk[h] c | rotated part), its value W_uv[h] c; the softmax denominator may hold a per-head sink, the head outputs
+    may be gated by sigmoid(W_g x)[h] (csrc/latent_attention.cu, absorbed form: W_uk is folded into the query, W_uv applied after the sum).
+
+    weights: q [H (dn + rot_dim), D] (per head: dn unrotated then rot_dim rotated), dkv [rank + rot_dim, D] and dkv.norm [rank] (absent when
+    ``shared``: the layer then attends over the cache another layer writes), uk [H dn, rank], uv [H dv, rank], o [D, H dv]; optional sink [H], g [H, D].
+    rot = dict(base, scaling) or None (the rotation always spans the whole rot_dim part); window = 0 for none."""
+    kind = "kv"
+
+    def __init__(self, w: Dict[str, torch.Tensor], heads: int, dn: int, rot_dim: int, dv: int, rank: int, scale: float, eps: float, dtype: torch.dtype,
+                 rot: Optional[dict] = None, shared: bool = False, window: int = 0, block_size: int = 64, max_pos: int = 4096):
+        if rot_dim % 2:
+            raise BackendError(f"LatentAttentionMixer: the rotated part has {rot_dim} entries, not an even number")
+        self.H, self.dn, self.dr, self.dv, self.R, self.scale, self.eps, self.dtype = heads, dn, rot_dim, dv, rank, float(scale), eps, dtype
+        self.shared, self.window, self.block_size, self.rot = bool(shared), int(window), block_size, rot
+        parts = [w["q"]]
+        self.off_dkv = heads * (dn + rot_dim)
+        self.off_g = self.off_dkv
+        if not shared:
+            parts.append(w["dkv"])
+            self.off_g += rank + rot_dim
+        self.has_gate = "g" in w
+        if self.has_gate:
+            parts.append(w["g"])
+        self.w_in = torch.cat(parts, 0).to(dtype).contiguous()
+        want = {"q": (heads * (dn + rot_dim),), "uk": (heads * dn, rank), "uv": (heads * dv, rank), "o": (None, heads * dv)}
+        if not shared:
+            want["dkv"] = (rank + rot_dim,)
+        for name, shape in want.items():
+            got = tuple(w[name].shape)
+            if any(s is not None and s != g for s, g in zip(shape, got)):
+                raise BackendError(f"LatentAttentionMixer: {name} is {got}, expected {shape}")
+        self.c_norm = None if shared or "dkv.norm" not in w else w["dkv.norm"].float().contiguous()
+        self.sink = w["sink"].float().contiguous() if "sink" in w else None
+        self.w_uk = w["uk"].to(dtype).contiguous()
+        self.w_uv = w["uv"].to(dtype).contiguous()
+        self.w_o = w["o"].to(dtype).contiguous()
+        self.cos = self.sin = None
+        self._device = self.w_in.device
+        if rot and rot_dim:
+            self.ensure_positions(max_pos)
+
+    def ensure_positions(self, max_pos: int) -> None:
+        if self.rot and self.dr and (self.cos is None or self.cos.shape[0] < max_pos):
+            self.cos, self.sin = yarn_rotary_tables(self.dr, float(self.rot["base"]), max_pos, self.rot.get("scaling"), self._device)
+
+    def cache_shape(self):
+        return (1, self.R, max(self.dr, 1))             # "keys" = latents, "values" = the shared rotated key part
+
+    def forward(self, h: torch.Tensor, batch: StepBatch, cache) -> torch.Tensor:
+        c_cache, kr_cache = cache
+        if self.cos is not None and batch.max_position >= self.cos.shape[0]:
+            self.ensure_positions(max(2 * self.cos.shape[0], batch.max_position + 1))
+        proj = ops.linear(h, self.w_in)
+        if not self.shared:
+            ops.latent_kv_rope_cache(proj, self.off_dkv, self.c_norm, self.cos, self.sin, batch, c_cache, kr_cache, self.R, self.dr, self.eps)
+        q_lat = ops.latent_q_absorb(proj, self.w_uk, self.cos, self.sin, batch, self.H, self.dn, self.dr, self.R)
+        o_lat = ops.latent_attention_varlen(q_lat, c_cache, kr_cache, batch, self.sink, self.H, self.R, self.dr, self.block_size, self.scale, self.window)
+        a = ops.latent_out_gate(o_lat, self.w_uv, proj[:, self.off_g:] if self.has_gate else None, self.H, self.dv, self.R, self.dtype)
+        return ops.linear(a, self.w_o)
+
+
+class RoutedExperts:
+    """Mixture of experts with a softmax router: down(silu(gate x) * (up x)) per expert, weights e<j>.gate / e<j>.up [ff, D], e<j>.down [D, ff],
+    router [N, D], optional correction [N] (added to the scores for the choice only).  N = experts + identity: the last ``identity`` router outputs
+    are experts without weights whose output is the input itself.  ``groups`` / ``keep`` restrict the choice to the best groups of neighbouring
+    outputs (0 = off); the chosen scores are normalised and multiplied by ``scale`` (csrc/moe_ragged.cu)."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], experts: int, identity: int, top: int, scale: float, dtype: torch.dtype, groups: int = 0, keep: int = 0):
+        self.E, self.I, self.top, self.scale, self.groups, self.keep, self.dtype = experts, identity, top, float(scale), int(groups), int(keep), dtype
+        self.N = experts + identity
+        if tuple(w["router"].shape)[0] != self.N:
+            raise BackendError(f"RoutedExperts: the router has {w['router'].shape[0]} outputs, expected {experts} + {identity}")
+        if top > self.N or (self.groups > 1 and (self.N % self.groups or not 0 < self.keep <= self.groups)):
+            raise BackendError(f"RoutedExperts: top {top} / groups {groups} / keep {keep} do not fit {self.N} router outputs")
+        self.router = w["router"].to(dtype).contiguous()
+        self.correction = w["correction"].float().contiguous() if "correction" in w else None
+        self.w_gu = self.w_d = None
+        self.ff = 0
+        if experts:
+            self.w_gu = torch.stack([torch.cat([w[f"e{j}.gate"], w[f"e{j}.up"]], 0) for j in range(experts)], 0).to(dtype).contiguous()
+            self.w_d = torch.stack([w[f"e{j}.down"] for j in range(experts)], 0).to(dtype).contiguous()
+            self.ff = self.w_d.shape[2]
+
+    def forward(self, h: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """h: the input in the compute dtype, x: the same rows in f32 (what an identity expert returns)"""
+        ids, wts = ops.moe_route(ops.linear(h, self.router), self.correction, self.top, self.groups, self.keep, self.scale)
+        act = ops.moe_gate_up(h, self.w_gu, ids) if self.E else None
+        return ops.moe_down_combine(act, self.w_d, ids, wts, x, self.E, self.ff)
+
+
+class TokenSideInput:
+    """A per-layer, per-token embedding let in by the stream: e = table[token, col0 : col0 + dim]; y = proj (gelu_tanh(gate x) * e);
+    x <- x + rms_norm(y) * norm.  weights: gate [dim, D], proj [D, dim], norm [D]; the table [vocab, layers * dim] is shared by the layers."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], table: torch.Tensor, col0: int, dim: int, eps: float, dtype: torch.dtype):
+        self.table, self.col0, self.dim, self.eps = table, int(col0), int(dim), eps
+        self.w_gate = w["gate"].to(dtype).contiguous()
+        self.w_proj = w["proj"].to(dtype).contiguous()
+        self.norm = w["norm"].float().contiguous()
+
+    def forward(self, x: torch.Tensor, h: torch.Tensor, batch: StepBatch, out16: Optional[torch.Tensor]) -> None:
+        g = ops.gelu_tanh_gather_mul(ops.linear(h, self.w_gate), self.table, self.col0, batch.tokens, self.dim)
+        ops.residual_rms_norm(x, ops.linear(g, self.w_proj), self.norm, 1.0, self.eps, False, out16)

@@ -42,10 +42,16 @@ def _gobesun(path, **kw):
     return GobesunModel.from_pretrained(path, **kw)
 
 
+def _guvusun(path, **kw):
+    from .guvusun import GuvusunModel
+    return GuvusunModel.from_pretrained(path, **kw)
+
+
 def _llama(path, **kw):
     from .llama import load_dense_checkpoint
     return load_dense_checkpoint(path, **kw)
 
 
 register_model("Gobesun", _gobesun)
+register_model("Guvusun", _guvusun)
 register_model("LlamaForCausalLM", _llama)

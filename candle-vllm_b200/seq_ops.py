@@ -220,3 +220,131 @@ def paged_attention_decode_chunked(q: torch.Tensor, k_cache: torch.Tensor, v_cac
                              C.c_size_t(ws.numel()), _stream(q.device))
     check("paged_attention_decode_chunked")
     return out
+
+
+# ---- latent attention, routed experts, post-sum norms -----------------------------------------------------------------------------------
+
+def embedding_bigram(table: torch.Tensor, bigram: Optional[torch.Tensor], batch: StepBatch, prev_state: Optional[torch.Tensor], buckets: int, mul_prev: int,
+                     mul_cur: int) -> torch.Tensor:
+    """table[token] + bigram[hash(previous token, token)] -> f32 [T, dim]; ``prev_state`` i32 [slots, 1] carries each sequence's last token
+    from step to step (read for an entry's first row, then set to the entry's last token)."""
+    vocab, dim = table.shape
+    T = batch.tokens.shape[0]
+    out = torch.empty((T, dim), dtype=torch.float32, device=table.device)
+    if bigram is not None and (bigram.dtype != table.dtype or bigram.shape != (buckets + 1, dim) or prev_state is None or prev_state.dtype != torch.int32):
+        raise BackendError(f"embedding_bigram: bigram table {tuple(bigram.shape)} for {buckets} buckets, or no i32 previous-token state")
+    lib().embedding_bigram(_ptr(table), _ptr(bigram), _ptr(batch.tokens), _ptr(batch.positions), _ptr(batch.token_seq), _ptr(batch.cu_seqlens),
+                           _ptr(batch.seq_slots), _ptr(prev_state), _ptr(out), C.c_int32(T), C.c_int32(dim), C.c_int32(vocab), C.c_int32(buckets),
+                           C.c_int32(mul_prev), C.c_int32(mul_cur), C.c_int32(_tag(table.dtype)), _stream(table.device))
+    check("embedding_bigram")
+    return out
+
+
+def residual_rms_norm(x: torch.Tensor, y: Optional[torch.Tensor], weight: torch.Tensor, alpha: float, eps: float, after_sum: bool,
+                      out16: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """In place on the f32 stream x [T, n]: ``after_sum`` x <- norm(alpha x + y) * w (y None = no sublayer output), else x <- x + norm(y) * w.
+    ``out16`` (bf16 [T, n]) also receives the new x."""
+    T, n = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or weight.dtype != torch.float32 or (y is not None and (y.dtype != torch.float32 or y.stride(1) != 1)):
+        raise BackendError("residual_rms_norm: f32 tensors, x contiguous")
+    if out16 is not None and (out16.dtype != torch.bfloat16 or not out16.is_contiguous() or out16.shape != x.shape):
+        raise BackendError("residual_rms_norm: out16 is bf16 of x's shape")
+    lib().residual_rms_norm(_ptr(x), _ptr(y), C.c_int64(0 if y is None else (y.stride(0) if T > 1 else max(n, y.stride(0)))), _ptr(weight), _ptr(out16), C.c_int32(T),
+                            C.c_int32(n), C.c_float(alpha), C.c_float(eps), C.c_int32(0 if after_sum else 1), _stream(x.device))
+    check("residual_rms_norm")
+    return x
+
+
+def gelu_tanh_gather_mul(z: torch.Tensor, table: torch.Tensor, col0: int, ids: torch.Tensor, dim: int) -> torch.Tensor:
+    """gelu_tanh(z[t, :dim]) * table[ids[t], col0 : col0 + dim] -> [T, dim] of the table's dtype"""
+    T = z.shape[0]
+    out = torch.empty((T, dim), dtype=table.dtype, device=z.device)
+    lib().gelu_tanh_gather_mul(_ptr(z), C.c_int64(z.stride(0) if T > 1 else max(dim, z.stride(0))), _ptr(table), C.c_int64(table.stride(0)), C.c_int32(col0), _ptr(ids),
+                               _ptr(out), C.c_int32(T), C.c_int32(dim), C.c_int32(table.shape[0]), C.c_int32(_tag(table.dtype)), C.c_int32(_tag(table.dtype)),
+                               _stream(z.device))
+    check("gelu_tanh_gather_mul")
+    return out
+
+
+def latent_kv_rope_cache(proj: torch.Tensor, off: int, norm_w: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], batch: StepBatch,
+                         c_cache: torch.Tensor, kr_cache: torch.Tensor, rank: int, rot_dim: int, eps: float) -> None:
+    T = proj.shape[0]
+    if cos is not None and batch.max_position >= cos.shape[0]:
+        raise BackendError(f"position {batch.max_position} is outside the rotary table ({cos.shape[0]} rows)")
+    lib().latent_kv_rope_cache(_ptr(proj), C.c_int64(proj.stride(0) if T > 1 else proj.shape[1]), C.c_int32(off), _ptr(norm_w), _ptr(cos), _ptr(sin),
+                               C.c_int32(0 if cos is None else cos.shape[0]), _ptr(batch.positions), _ptr(batch.slot_mapping), _ptr(c_cache), _ptr(kr_cache),
+                               C.c_int32(T), C.c_int32(rank), C.c_int32(rot_dim), C.c_float(eps), C.c_int32(_tag(c_cache.dtype)), _stream(proj.device))
+    check("latent_kv_rope_cache")
+
+
+def latent_q_absorb(proj: torch.Tensor, w_uk: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], batch: StepBatch, heads: int,
+                    dn: int, rot_dim: int, rank: int, q_lat: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """-> q_lat f32 [T, H, rank + rot_dim]; w_uk None writes only the rotated part (the caller fills [..., :rank])"""
+    T = proj.shape[0]
+    if cos is not None and batch.max_position >= cos.shape[0]:
+        raise BackendError(f"position {batch.max_position} is outside the rotary table ({cos.shape[0]} rows)")
+    if q_lat is None:
+        q_lat = torch.empty((T, heads, rank + rot_dim), dtype=torch.float32, device=proj.device)
+    lib().latent_q_absorb(_ptr(proj), C.c_int64(proj.stride(0) if T > 1 else proj.shape[1]), _ptr(w_uk), _ptr(cos), _ptr(sin), C.c_int32(0 if cos is None else cos.shape[0]),
+                          _ptr(batch.positions), _ptr(q_lat), C.c_int32(T), C.c_int32(heads), C.c_int32(dn), C.c_int32(rot_dim), C.c_int32(rank),
+                          C.c_int32(_tag(w_uk.dtype) if w_uk is not None else DType.F32), _stream(proj.device))
+    check("latent_q_absorb")
+    return q_lat
+
+
+def latent_attention_varlen(q_lat: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor, batch: StepBatch, sink: Optional[torch.Tensor], heads: int,
+                            rank: int, rot_dim: int, block_size: int, scale: float, window: int = 0) -> torch.Tensor:
+    T = q_lat.shape[0]
+    o = torch.empty((T, heads, rank), dtype=torch.float32, device=q_lat.device)
+    lib().latent_attention_varlen(_ptr(o), _ptr(q_lat), _ptr(c_cache), _ptr(kr_cache), _ptr(batch.block_tables), C.c_int32(batch.block_tables.shape[1]),
+                                  _ptr(batch.token_seq), _ptr(batch.positions), _ptr(sink), C.c_int32(T), C.c_int32(heads), C.c_int32(rank), C.c_int32(rot_dim),
+                                  C.c_int32(block_size), C.c_float(scale), C.c_int32(window), C.c_int32(_tag(c_cache.dtype)), _stream(q_lat.device))
+    check("latent_attention_varlen")
+    return o
+
+
+def latent_out_gate(src: torch.Tensor, w_uv: Optional[torch.Tensor], gate: Optional[torch.Tensor], heads: int, dv: int, rank: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """sigmoid(gate[t, h]) * (w_uv[h] src[t, h]) -> [T, H dv]; w_uv None: src is [T, H, dv] already"""
+    T = src.shape[0]
+    out = torch.empty((T, heads * dv), dtype=out_dtype, device=src.device)
+    lib().latent_out_gate(_ptr(src), _ptr(w_uv), _ptr(gate), C.c_int64(0 if gate is None else (gate.stride(0) if T > 1 else max(heads, gate.stride(0)))), _ptr(out),
+                          C.c_int32(T), C.c_int32(heads), C.c_int32(dv), C.c_int32(rank), C.c_int32(_tag(w_uv.dtype) if w_uv is not None else _tag(out_dtype)),
+                          C.c_int32(_tag(out_dtype)), _stream(src.device))
+    check("latent_out_gate")
+    return out
+
+
+def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int, scale: float):
+    """f32 [T, N] -> (ids i32 [T, top], weights f32 [T, top])"""
+    T, N = logits.shape
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    lib().moe_route(_ptr(logits), C.c_int64(logits.stride(0) if T > 1 else max(N, logits.stride(0))), _ptr(correction), _ptr(ids), _ptr(w), C.c_int32(T), C.c_int32(N),
+                    C.c_int32(top), C.c_int32(groups), C.c_int32(keep), C.c_float(scale), _stream(logits.device))
+    check("moe_route")
+    return ids, w
+
+
+def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """h [T, D], w_gate_up [E, 2 ff, D] of one dtype -> act [T * top, ff] (rows of identity choices are left unwritten)"""
+    T, D = h.shape
+    E, ff2, _ = w_gate_up.shape
+    top = ids.shape[1]
+    act = torch.empty((T * top, ff2 // 2), dtype=h.dtype, device=h.device)
+    lib().moe_gate_up(_ptr(h), C.c_int64(h.stride(0) if T > 1 else max(D, h.stride(0))), _ptr(w_gate_up), _ptr(ids), _ptr(act), C.c_int32(T), C.c_int32(top), C.c_int32(E),
+                      C.c_int32(ff2 // 2), C.c_int32(D), C.c_int32(_tag(h.dtype)), _stream(h.device))
+    check("moe_gate_up")
+    return act
+
+
+def moe_down_combine(act: Optional[torch.Tensor], w_down: Optional[torch.Tensor], ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, num_experts: int,
+                     ff: int) -> torch.Tensor:
+    """-> f32 [T, D]: the weighted sum of the chosen experts' outputs, identity choices contributing weight * x"""
+    T, D = x.shape
+    top = ids.shape[1]
+    out = torch.empty((T, D), dtype=torch.float32, device=x.device)
+    dt = _tag(w_down.dtype) if w_down is not None else DType.F32
+    lib().moe_down_combine(_ptr(act), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(x), C.c_int64(x.stride(0) if T > 1 else max(D, x.stride(0))), _ptr(out), C.c_int32(T),
+                           C.c_int32(top), C.c_int32(num_experts), C.c_int32(ff), C.c_int32(D), C.c_int32(dt), _stream(x.device))
+    check("moe_down_combine")
+    return out

@@ -47,15 +47,17 @@ class SlotPool:
 
 
 class StateCache:
-    """Device tensors of the recurrent layers: for layer run i a tuple of f32 tensors whose leading dimension is the slot.
-    ``shapes[i]`` = tuple of per-slot shapes (e.g. ((taps - 1, channels), (heads, dk, dv)))."""
+    """Device tensors of the recurrent layers: for layer run i a tuple of tensors whose leading dimension is the slot.
+    ``shapes[i]`` = tuple of per-slot shapes (e.g. ((taps - 1, channels), (heads, dk, dv))), f32 unless an entry is a (shape, dtype) pair
+    (integer state such as a sequence's last token)."""
 
     def __init__(self, shapes: Sequence[Sequence[Tuple[int, ...]]], num_slots: int, device="cuda"):
         self.num_slots = int(num_slots)
         self.pool = SlotPool(num_slots)
         self.scratch_slot = self.num_slots          # one slot past the pool: a place for warm-up steps to write
+        typed = lambda s: (tuple(s[0]), s[1]) if len(s) == 2 and isinstance(s[1], torch.dtype) else (tuple(s), torch.float32)
         self.tensors: List[Tuple[torch.Tensor, ...]] = [
-            tuple(torch.zeros((self.num_slots + 1,) + tuple(s), dtype=torch.float32, device=device) for s in per_layer) for per_layer in shapes]
+            tuple(torch.zeros((self.num_slots + 1,) + typed(s)[0], dtype=typed(s)[1], device=device) for s in per_layer) for per_layer in shapes]
 
     def bytes_per_slot(self) -> int:
-        return sum(t[0].numel() * 4 for per in self.tensors for t in per)
+        return sum(t[0].numel() * t.element_size() for per in self.tensors for t in per)

@@ -476,6 +476,52 @@ long long b200_total_kernel_launches(void);
  * src/openai/distributed.rs:547-654) */
 void b200_allreduce_f32(void* nccl_comm, float* buf, int64_t n, int64_t stream);
 
+/* ---- latent attention, routed experts and post-sum norms for ragged steps (csrc/latent_attention.cu, moe_ragged.cu, norm_act.cu) -------------
+ * embedding_bigram: out f32 [T, dim] = table[ids[t]] + bigram[row(t)], row = (previous token * mul_prev + token * mul_cur) mod buckets, row
+ *   `buckets` for a token at position 0; the previous token of an entry's first row is prev_state[seq_slots[b]] (i32 per state slot), which then
+ *   takes the entry's last token.  bigram may be null.
+ * residual_rms_norm: in place on the f32 stream x [rows, n]: mode 0 x <- (alpha x + y) / rms * w (y may be null), mode 1 x <- x + y / rms(y) * w;
+ *   out16 (optional, bf16 [rows, n]) receives the new x as well.
+ * gelu_tanh_gather_mul: out[t, i] = gelu_tanh(z[t, i]) * table[ids[t], col0 + i], i < dim; table and out of one dtype (F32 / BF16).
+ * latent_kv_rope_cache: columns [off, off + rank + rot_dim) of proj f32 [T, ld]: RMS norm (weight f32 [rank] or null) of the first rank -> c_cache
+ *   [slots, rank]; the last rot_dim rotated (entry i with i + rot_dim/2; cos / sin f32 [max_pos, rot_dim/2]) -> kr_cache [slots, rot_dim]; slot =
+ *   slot_mapping[t] (negative = skip); cache_dtype F32 / BF16.
+ * latent_q_absorb: proj holds q as [H, dn | rot_dim] per token; q_lat f32 [T, H, rank + rot_dim] = (w_uk[h]^T q_n | rotated q_r), w_uk [H dn, rank] of
+ *   w_dtype; w_uk null = only the rotated part is written.
+ * latent_attention_varlen: o_lat f32 [T, H, rank] = sum_j p_j c_j over the keys j <= positions[t] (and positions[t] - j < window when window > 0) of the
+ *   token's sequence, p = softmax of (q_lat . (c_j | kr_j)) * scale whose denominator also holds exp(sink[h]) (sink f32 [H] or null).  rank <= 1024.
+ * latent_out_gate: out [T, H, dv] = sigmoid(gate[t, h]) * (w_uv[h] src[t, h]), w_uv [H dv, rank], src f32 [T, H, rank]; w_uv null: src is f32
+ *   [T, H, dv] already; gate f32 (row pitch ld_gate) or null.
+ * moe_route: logits f32 [T, N] -> ids i32 [T, top], weights f32 [T, top]: softmax over N; choice = softmax + correction (f32 [N] or null); only
+ *   members of the `keep` groups (of `groups` equal runs of neighbours) with the best single choice score may be taken; weights = softmax of the
+ *   taken / (their sum + 1e-20) * scale.  groups <= 1: no restriction.
+ * moe_gate_up: act [T top, ff] = silu(W_gate[e] h_t) * (W_up[e] h_t) for every pair with e = ids[p] < num_experts; w_gate_up [E, 2 ff, width].
+ * moe_down_combine: out f32 [T, width] = sum_k weights[t, k] * (W_down[e] act[t, k]) (e < num_experts) or weights[t, k] * x[t] (identity expert);
+ *   w_down [E, width, ff]. */
+void embedding_bigram(const void* table, const void* bigram, const int32_t* ids, const int32_t* positions, const int32_t* token_seq,
+                      const int32_t* cu_seqlens, const int32_t* seq_slots, int32_t* prev_state, float* out, int32_t num_tokens, int32_t dim,
+                      int32_t vocab, int32_t buckets, int32_t mul_prev, int32_t mul_cur, int32_t table_dtype, int64_t stream);
+void residual_rms_norm(float* x, const float* y, int64_t ldy, const float* weight, void* out16, int32_t rows, int32_t n, float alpha, float eps,
+                       int32_t mode, int64_t stream);
+void gelu_tanh_gather_mul(const float* z, int64_t ldz, const void* table, int64_t ld_table, int32_t col0, const int32_t* ids, void* out, int32_t rows,
+                          int32_t dim, int32_t vocab, int32_t table_dtype, int32_t out_dtype, int64_t stream);
+void latent_kv_rope_cache(const float* proj, int64_t ld, int32_t off, const float* norm_w, const float* cos_t, const float* sin_t, int32_t max_pos,
+                          const int32_t* positions, const int64_t* slot_mapping, void* c_cache, void* kr_cache, int32_t num_tokens, int32_t rank,
+                          int32_t rot_dim, float eps, int32_t cache_dtype, int64_t stream);
+void latent_q_absorb(const float* proj, int64_t ld, const void* w_uk, const float* cos_t, const float* sin_t, int32_t max_pos, const int32_t* positions,
+                     float* q_lat, int32_t num_tokens, int32_t num_heads, int32_t dn, int32_t rot_dim, int32_t rank, int32_t w_dtype, int64_t stream);
+void latent_attention_varlen(float* o_lat, const float* q_lat, const void* c_cache, const void* kr_cache, const int32_t* block_tables, int32_t table_width,
+                             const int32_t* token_seq, const int32_t* positions, const float* sink, int32_t num_tokens, int32_t num_heads, int32_t rank,
+                             int32_t rot_dim, int32_t block_size, float scale, int32_t window, int32_t cache_dtype, int64_t stream);
+void latent_out_gate(const float* src, const void* w_uv, const float* gate, int64_t ld_gate, void* out, int32_t num_tokens, int32_t num_heads, int32_t dv,
+                     int32_t rank, int32_t w_dtype, int32_t out_dtype, int64_t stream);
+void moe_route(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* weights, int32_t num_tokens, int32_t num_outputs, int32_t top,
+               int32_t groups, int32_t keep, float scale, int64_t stream);
+void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, void* act, int32_t num_tokens, int32_t top, int32_t num_experts,
+                 int32_t ff, int32_t width, int32_t dtype, int64_t stream);
+void moe_down_combine(const void* act, const void* w_down, const int32_t* ids, const float* weights, const float* x, int64_t ldx, float* out,
+                      int32_t num_tokens, int32_t top, int32_t num_experts, int32_t ff, int32_t width, int32_t dtype, int64_t stream);
+
 #ifdef __cplusplus
 }
 #endif
