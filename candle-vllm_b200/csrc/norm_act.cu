@@ -96,7 +96,7 @@ embedding_bigram_kernel(const TTab* __restrict__ table, const TTab* __restrict__
         if (t == first) {
             // only this block touches the entry's slot: read what the last step left, then leave the entry's last token
             const int slot = seq_slots[b];
-            if (slot >= 0) {
+            if (prev_state && slot >= 0) {
                 if (positions[t] > 0) prev = prev_state[slot];
                 prev_state[slot] = ids[last];
             }

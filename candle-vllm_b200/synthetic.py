@@ -255,3 +255,77 @@ def gobesun_weights(cfg: dict, seed: int = 0, device="cpu") -> dict:
             out[p + "norm2"], out[p + "norm2b"] = rnd(D, std=0.2), rnd(D, std=0.2)
             out[p + "mlp.gate"], out[p + "mlp.up"], out[p + "mlp.down"] = lin(ff, D), lin(ff, D), lin(D, ff)
     return {k: v.to(torch.bfloat16).to(device) for k, v in out.items()}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Guvusun: random checkpoints of any shape (tests and bench.py)
+# ---------------------------------------------------------------------------------------------------------------------
+def guvusun_layer(heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, experts: int = 0, ff: int = 0, top: int = 1, identity: int = 0,
+                  groups: tuple = None, router_scale: float = 1.0, kv_from: int = None, base: float = 10000.0, scaling: dict = None, scale: float = None) -> dict:
+    rot = dict(base=base, dims=rot_dim)
+    if scaling:
+        rot["scaling"] = scaling
+    mixer = dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, rot=rot, scale=(dim + rot_dim) ** -0.5 if scale is None else scale)
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    mlp = None
+    if experts or identity:
+        router = dict(experts=experts, top=top, scale=router_scale)
+        if identity:
+            router["identity"] = identity
+        if groups:
+            router["groups"] = dict(count=groups[0], keep=groups[1])
+        mlp = dict(kind="moe", expert=dict(ff=ff), router=router)
+    return dict(type="latent_attention", mixer=mixer, mlp=mlp)
+
+
+def guvusun_config(width: int, vocab: int, layers: list, alpha: float = 1.5, bigram: dict = None, side_dim: int = 0, eps: float = 1e-6) -> dict:
+    cfg = dict(architecture="Guvusun", layers=layers, norm=dict(eps=eps), postln_alpha=alpha, vocab=vocab, width=width)
+    if bigram:
+        cfg["embedding"] = dict(bigram=dict(bigram))
+    if side_dim:
+        cfg["token_side"] = dict(dim=side_dim)
+    return cfg
+
+
+def guvusun_weights(cfg: dict, seed: int = 0, device="cpu") -> dict:
+    """name -> bf16 tensor with magnitudes that keep every mechanism visible in the logits: sinks of the order of the scores, corrections large
+    enough to change the router's choice (and negative on average), a peaked router."""
+    g = torch.Generator().manual_seed(seed)
+    D, V = cfg["width"], cfg["vocab"]
+    out = {}
+    rnd = lambda *shape, std=1.0: (torch.randn(*shape, generator=g) * std)
+    lin = lambda n, k, gain=1.0: rnd(n, k, std=gain * k ** -0.5)
+    out["embed"] = rnd(V, D)
+    bg = (cfg.get("embedding") or {}).get("bigram")
+    if bg:
+        out["bigram"] = rnd(bg["buckets"] + 1, D, std=0.7)
+    out["embed.norm"] = 1.0 + rnd(D, std=0.2)
+    out["head"] = lin(V, D)
+    out["final.norm"] = 1.0 + rnd(D, std=0.2)
+    side = int((cfg.get("token_side") or {}).get("dim", 0))
+    if side:
+        out["side.embed"] = rnd(V, side * len(cfg["layers"]))
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+        out[p + "norm1"] = 1.0 + rnd(D, std=0.2)
+        out[p + "mix.q"] = lin(H * (dn + dr), D, 1.5)
+        if m.get("kv_from") is None:
+            out[p + "mix.dkv"] = lin(R + dr, D)
+            out[p + "mix.dkv.norm"] = 1.0 + rnd(R, std=0.3)
+        out[p + "mix.uk"], out[p + "mix.uv"] = lin(H * dn, R, 1.5), lin(H * dv, R)
+        out[p + "mix.sink"] = rnd(H, std=1.5)
+        out[p + "mix.g"] = lin(H, D, 2.0)
+        out[p + "mix.o"] = lin(D, H * dv)
+        if L.get("mlp"):
+            r = L["mlp"]["router"]
+            E, I, ff = r["experts"], r.get("identity", 0), L["mlp"]["expert"]["ff"]
+            out[p + "norm2"] = 1.0 + rnd(D, std=0.2)
+            out[p + "mlp.router"] = lin(E + I, D, 3.0)
+            out[p + "mlp.correction"] = rnd(E + I, std=0.15) - 0.4
+            for j in range(E):
+                out[p + f"mlp.e{j}.gate"], out[p + f"mlp.e{j}.up"], out[p + f"mlp.e{j}.down"] = lin(ff, D), lin(ff, D), lin(D, ff)
+        if side:
+            out[p + "side.gate"], out[p + "side.proj"], out[p + "side.norm"] = lin(side, D), lin(D, side), 0.5 + rnd(D, std=0.1)
+    return {k: v.to(torch.bfloat16).to(device) for k, v in out.items()}

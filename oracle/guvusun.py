@@ -42,10 +42,12 @@ def bigram_rows(tokens: List[int], buckets: int, mul_prev: int, mul_cur: int) ->
     return rows
 
 
-def embed(tokens: List[int], table: torch.Tensor, bigram: torch.Tensor, norm_w: torch.Tensor, bg: dict, eps: float) -> torch.Tensor:
-    idx = torch.tensor(tokens, dtype=torch.long)
-    rows = torch.tensor(bigram_rows(tokens, int(bg["buckets"]), int(bg["mul_prev"]), int(bg["mul_cur"])), dtype=torch.long)
-    return rms(table.to(F)[idx] + bigram.to(F)[rows], eps) * norm_w.to(F)
+def embed(tokens: List[int], table: torch.Tensor, bigram: Optional[torch.Tensor], norm_w: torch.Tensor, bg: Optional[dict], eps: float) -> torch.Tensor:
+    x = table.to(F)[torch.tensor(tokens, dtype=torch.long)]
+    if bg:
+        rows = torch.tensor(bigram_rows(tokens, int(bg["buckets"]), int(bg["mul_prev"]), int(bg["mul_cur"])), dtype=torch.long)
+        x = x + bigram.to(F)[rows]
+    return rms(x, eps) * norm_w.to(F)
 
 
 def rotary_angles(T: int, dims: int, base: float, scaling: Optional[dict]):
@@ -99,13 +101,14 @@ def latent_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: 
     v = (c @ g("uv").T).reshape(T, H, dv)
     s = (torch.einsum("ihd,jhd->hij", qn, kn) + torch.einsum("ihd,jd->hij", qr, kr)) * float(m["scale"])
     s = s.masked_fill(~torch.tril(torch.ones(T, T, dtype=torch.bool)), float("-inf"))
-    sink = g("sink")[:, None, None]
+    sink = g("sink")[:, None, None] if "sink" in w else torch.full((H, 1, 1), float("-inf"), dtype=F)
     mx = torch.maximum(s.max(-1, keepdim=True).values, sink)
     e = torch.exp(s - mx)
-    p = e / (e.sum(-1, keepdim=True) + torch.exp(sink - mx))
+    p = e / (e.sum(-1, keepdim=True) + torch.exp(sink - mx))      # the sink adds to the denominator and to nothing else
     o = torch.einsum("hij,jhd->ihd", p, v)
-    gate = torch.sigmoid(h @ g("g").T)                       # [T, H]
-    o = (o * gate[..., None]).reshape(T, H * dv)
+    if "g" in w:
+        o = o * torch.sigmoid(h @ g("g").T)[..., None]          # one gate per token and head
+    o = o.reshape(T, H * dv)
     return o @ g("o").T, (c, kr)
 
 
@@ -114,7 +117,7 @@ def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, r: 
     single member; weights use the plain softmax of the chosen, normalised, times the scale."""
     n_all, top = w_router.shape[0], int(r["top"])
     s = torch.softmax(h @ w_router.to(F).T, -1)
-    pick = s + correction.to(F)
+    pick = s if correction is None else s + correction.to(F)
     groups = r.get("groups")
     if groups:
         cnt, keep = int(groups["count"]), int(groups["keep"])
@@ -134,7 +137,7 @@ def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict) -> torch.Tensor:
     # "experts" counts the experts that have weights; the identity experts are the last router outputs
     if w["router"].shape[0] != n_all:
         raise ValueError("router rows != experts + identity")
-    ids, ws = route(h, w["router"], w["correction"], r)
+    ids, ws = route(h, w["router"], w.get("correction"), r)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(ids[t].tolist(), ws[t]):
@@ -156,7 +159,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], hidden: Op
     """-> logits [T, vocab]; ``hidden`` collects the stream after every layer"""
     eps, alpha = float(cfg["norm"]["eps"]), float(cfg["postln_alpha"])
     sub = lambda pre: {k[len(pre):]: v for k, v in w.items() if k.startswith(pre)}
-    x = embed(tokens, w["embed"], w["bigram"], w["embed.norm"], cfg["embedding"]["bigram"], eps)
+    bg = (cfg.get("embedding") or {}).get("bigram")
+    x = embed(tokens, w["embed"], w.get("bigram"), w["embed.norm"], bg, eps)
     kept = {}
     for i, L in enumerate(cfg["layers"]):
         p = f"l{i}."
@@ -167,8 +171,18 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], hidden: Op
         x = rms(alpha * x + y, eps) * w[p + "norm1"].to(F)
         if L.get("mlp"):
             x = rms(alpha * x + moe(x, sub(p + "mlp."), L["mlp"]), eps) * w[p + "norm2"].to(F)
+        elif p + "norm2" in w:
+            x = rms(alpha * x, eps) * w[p + "norm2"].to(F)
         if cfg.get("token_side"):
             x = token_side(x, tokens, w["side.embed"], i, int(cfg["token_side"]["dim"]), sub(p + "side."), eps)
         if hidden is not None:
             hidden.append(x.clone())
     return (rms(x, eps) * w["final.norm"].to(F)) @ w["head"].to(F).T
+
+
+def greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    ids, out = list(prompt), []
+    for _ in range(n):
+        t = int(torch.argmax(forward(cfg, w, ids)[-1]))
+        out.append(t); ids.append(t)
+    return out
