@@ -58,13 +58,14 @@ latent_kv_rope_cache_kernel(const float* __restrict__ proj, int64_t ld, int off,
 template <typename TW>
 __global__ void __launch_bounds__(128)
 latent_q_absorb_kernel(const float* __restrict__ proj, int64_t ld, const TW* __restrict__ w_uk, const float* __restrict__ cos_t,
-                       const float* __restrict__ sin_t, const int32_t* __restrict__ positions, float* __restrict__ q_lat, int H, int dn, int dr, int R) {
+                       const float* __restrict__ sin_t, const int32_t* __restrict__ positions, float* __restrict__ q_lat, int64_t q_st, int64_t q_sh,
+                       __nv_bfloat16* __restrict__ qn16, int64_t rows16, int H, int dn, int dr, int R) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float qn[];                          // [dn]
     const int t = blockIdx.x, h = blockIdx.y;
     const float* q = proj + (int64_t)t * ld + (int64_t)h * (dn + dr);
-    float* o = q_lat + ((int64_t)t * H + h) * (R + dr);
+    float* o = q_lat + (int64_t)t * q_st + (int64_t)h * q_sh;
     const int half = dr >> 1;
     const int pos = positions[t];
     for (int i = threadIdx.x; i < dr; i += 128) {
@@ -77,6 +78,8 @@ latent_q_absorb_kernel(const float* __restrict__ proj, int64_t ld, const TW* __r
         }
         o[R + i] = v;
     }
+    if (qn16)                                              // [H, rows16, dn]: the unrotated part as the 16-bit operand of the grouped product
+        for (int i = threadIdx.x; i < dn; i += 128) qn16[((int64_t)h * rows16 + t) * dn + i] = __float2bfloat16_rn(q[i]);
     if (!w_uk) return;
     for (int i = threadIdx.x; i < dn; i += 128) qn[i] = q[i];
     __syncthreads();
@@ -88,12 +91,12 @@ latent_q_absorb_kernel(const float* __restrict__ proj, int64_t ld, const TW* __r
     }
 }
 
-template <typename TC, int NR>
+template <typename TC, typename TO, int NR>
 __global__ void __launch_bounds__(256)
-latent_attention_varlen_kernel(const float* __restrict__ q_lat, const TC* __restrict__ c_cache, const TC* __restrict__ kr_cache,
+latent_attention_varlen_kernel(const float* __restrict__ q_lat, int64_t q_st, int64_t q_sh, const TC* __restrict__ c_cache, const TC* __restrict__ kr_cache,
                                const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ token_seq,
-                               const int32_t* __restrict__ positions, const float* __restrict__ sink, float* __restrict__ o_lat, int H, int R, int dr,
-                               int block_size, float scale, int window, int groups_per_token) {
+                               const int32_t* __restrict__ positions, const float* __restrict__ sink, TO* __restrict__ o_lat, int64_t o_st, int64_t o_sh,
+                               int H, int R, int dr, int block_size, float scale, int window, int groups_per_token) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float sm[];
@@ -107,7 +110,7 @@ latent_attention_varlen_kernel(const float* __restrict__ q_lat, const TC* __rest
     const int pos = positions[t];
     const int32_t* table = block_tables + (int64_t)token_seq[t] * table_width;
     if (live) {
-        const float* q = q_lat + ((int64_t)t * H + h) * W;
+        const float* q = q_lat + (int64_t)t * q_st + (int64_t)h * q_sh;
         for (int i = lane; i < W; i += 32) qs[warp * W + i] = q[i] * scale;
     }
     int lo = 0;
@@ -168,14 +171,14 @@ latent_attention_varlen_kernel(const float* __restrict__ q_lat, const TC* __rest
 #pragma unroll
     for (int c = 0; c < NR; ++c) {
         const int i = lane + 32 * c;
-        if (i < R) o_lat[((int64_t)t * H + h) * R + i] = acc[c] * inv;
+        if (i < R) o_lat[(int64_t)t * o_st + (int64_t)h * o_sh + i] = from_f32<TO>(acc[c] * inv);
     }
 }
 
 template <typename TW, typename TOut>
 __global__ void __launch_bounds__(128)
-latent_out_gate_kernel(const float* __restrict__ src, const TW* __restrict__ w_uv, const float* __restrict__ gate, int64_t ld_gate,
-                       TOut* __restrict__ out, int H, int dv, int R) {
+latent_out_gate_kernel(const float* __restrict__ src, int64_t s_st, int64_t s_sh, const TW* __restrict__ w_uv, const float* __restrict__ gate,
+                       int64_t ld_gate, TOut* __restrict__ out, int H, int dv, int R) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float ol[];                          // [R]
@@ -183,11 +186,12 @@ latent_out_gate_kernel(const float* __restrict__ src, const TW* __restrict__ w_u
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float gv = gate ? 1.0f / (1.0f + expf(-gate[(int64_t)t * ld_gate + h])) : 1.0f;
     TOut* o = out + ((int64_t)t * H + h) * dv;
-    if (!w_uv) {                                           // src is already [T, H, dv]
-        for (int i = threadIdx.x; i < dv; i += 128) o[i] = from_f32<TOut>(src[((int64_t)t * H + h) * dv + i] * gv);
+    const float* sp = src + (int64_t)t * s_st + (int64_t)h * s_sh;
+    if (!w_uv) {                                           // src holds the dv values already
+        for (int i = threadIdx.x; i < dv; i += 128) o[i] = from_f32<TOut>(sp[i] * gv);
         return;
     }
-    for (int i = threadIdx.x; i < R; i += 128) ol[i] = src[((int64_t)t * H + h) * R + i];
+    for (int i = threadIdx.x; i < R; i += 128) ol[i] = sp[i];
     __syncthreads();
     const TW* w = w_uv + (int64_t)h * dv * R;               // [dv, R]
     for (int d = warp; d < dv; d += 4) {
@@ -225,25 +229,29 @@ void latent_kv_rope_cache(const float* proj, int64_t ld, int32_t off, const floa
 }
 
 void latent_q_absorb(const float* proj, int64_t ld, const void* w_uk, const float* cos_t, const float* sin_t, int32_t max_pos, const int32_t* positions,
-                     float* q_lat, int32_t num_tokens, int32_t num_heads, int32_t dn, int32_t rot_dim, int32_t rank, int32_t w_dtype, int64_t stream) {
+                     float* q_lat, int64_t q_stride_token, int64_t q_stride_head, void* qn16, int64_t rows16, int32_t num_tokens, int32_t num_heads, int32_t dn,
+                     int32_t rot_dim, int32_t rank, int32_t w_dtype, int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(proj && positions && q_lat, kErrBadArg, "latent_q_absorb: null pointer");
     B200_REQUIRE(num_heads > 0 && num_heads <= 65535 && dn > 0 && rank > 0 && rot_dim >= 0 && rot_dim % 2 == 0 && ld >= (int64_t)num_heads * (dn + rot_dim) &&
-                 (cos_t == nullptr) == (sin_t == nullptr) && (!cos_t || max_pos > 0) && dn <= 8192, kErrBadArg, "latent_q_absorb: bad sizes");
+                 (cos_t == nullptr) == (sin_t == nullptr) && (!cos_t || max_pos > 0) && dn <= 8192 && (!qn16 || rows16 >= num_tokens), kErrBadArg,
+                 "latent_q_absorb: bad sizes");
     cudaStream_t st = as_stream(stream);
     const size_t smem = (size_t)dn * sizeof(float);
     const dim3 grid(num_tokens, num_heads);
     if (w_dtype == B200_F32)
-        launch_pdl(latent_q_absorb_kernel<float>, grid, dim3(128), smem, st, proj, ld, (const float*)w_uk, cos_t, sin_t, positions, q_lat, num_heads, dn, rot_dim, rank);
+        launch_pdl(latent_q_absorb_kernel<float>, grid, dim3(128), smem, st, proj, ld, (const float*)w_uk, cos_t, sin_t, positions, q_lat, q_stride_token,
+                   q_stride_head, (__nv_bfloat16*)qn16, rows16, num_heads, dn, rot_dim, rank);
     else if (w_dtype == B200_BF16)
-        launch_pdl(latent_q_absorb_kernel<__nv_bfloat16>, grid, dim3(128), smem, st, proj, ld, (const __nv_bfloat16*)w_uk, cos_t, sin_t, positions, q_lat, num_heads,
-                   dn, rot_dim, rank);
+        launch_pdl(latent_q_absorb_kernel<__nv_bfloat16>, grid, dim3(128), smem, st, proj, ld, (const __nv_bfloat16*)w_uk, cos_t, sin_t, positions, q_lat, q_stride_token,
+                   q_stride_head, (__nv_bfloat16*)qn16, rows16, num_heads, dn, rot_dim, rank);
     else { set_error(kErrUnsupported, "latent_q_absorb: weight dtype %d (f32 / bf16)", w_dtype); return; }
     count_launch();
     check_launch("latent_q_absorb");
 }
 
-void latent_attention_varlen(float* o_lat, const float* q_lat, const void* c_cache, const void* kr_cache, const int32_t* block_tables, int32_t table_width,
+void latent_attention_varlen(void* o_lat, int64_t o_stride_token, int64_t o_stride_head, int32_t out_dtype, const float* q_lat, int64_t q_stride_token,
+                             int64_t q_stride_head, const void* c_cache, const void* kr_cache, const int32_t* block_tables, int32_t table_width,
                              const int32_t* token_seq, const int32_t* positions, const float* sink, int32_t num_tokens, int32_t num_heads, int32_t rank,
                              int32_t rot_dim, int32_t block_size, float scale, int32_t window, int32_t cache_dtype, int64_t stream) {
     if (num_tokens == 0) return;
@@ -257,35 +265,37 @@ void latent_attention_varlen(float* o_lat, const float* q_lat, const void* c_cac
     const size_t smem = ((size_t)nw * W + (size_t)32 * (W | 1)) * sizeof(float);
     B200_REQUIRE(smem <= 200 * 1024, kErrUnsupported, "latent_attention_varlen: latent + rotated size %d does not fit shared memory", W);
     const dim3 grid((unsigned)((int64_t)num_tokens * groups));
-#define LAV(TC, NR)                                                                                                                                 \
+#define LAV(TC, TO, NR)                                                                                                                             \
     do {                                                                                                                                            \
-        auto kern = latent_attention_varlen_kernel<TC, NR>;                                                                                         \
+        auto kern = latent_attention_varlen_kernel<TC, TO, NR>;                                                                                     \
         ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem);                                                                        \
-        launch_pdl(kern, grid, dim3(nw * 32), smem, st, q_lat, (const TC*)c_cache, (const TC*)kr_cache, block_tables, table_width, token_seq, positions, sink, \
-                   o_lat, num_heads, rank, rot_dim, block_size, scale, window, groups);                                                             \
+        launch_pdl(kern, grid, dim3(nw * 32), smem, st, q_lat, q_stride_token, q_stride_head, (const TC*)c_cache, (const TC*)kr_cache, block_tables, table_width,  \
+                   token_seq, positions, sink, (TO*)o_lat, o_stride_token, o_stride_head, num_heads, rank, rot_dim, block_size, scale, window, groups);  \
     } while (0)
-#define LAV_R(TC)                                                                                                                                   \
+#define LAV_R(TC, TO)                                                                                                                               \
     do {                                                                                                                                            \
-        if (rank <= 128) LAV(TC, 4); else if (rank <= 256) LAV(TC, 8); else if (rank <= 512) LAV(TC, 16); else LAV(TC, 32);                         \
+        if (rank <= 128) LAV(TC, TO, 4); else if (rank <= 256) LAV(TC, TO, 8); else if (rank <= 512) LAV(TC, TO, 16); else LAV(TC, TO, 32);         \
     } while (0)
-    if (cache_dtype == B200_F32) LAV_R(float);
-    else if (cache_dtype == B200_BF16) LAV_R(__nv_bfloat16);
-    else { set_error(kErrUnsupported, "latent_attention_varlen: cache dtype %d (f32 / bf16)", cache_dtype); return; }
+    if (cache_dtype == B200_F32 && out_dtype == B200_F32) LAV_R(float, float);
+    else if (cache_dtype == B200_BF16 && out_dtype == B200_F32) LAV_R(__nv_bfloat16, float);
+    else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16) LAV_R(__nv_bfloat16, __nv_bfloat16);
+    else { set_error(kErrUnsupported, "latent_attention_varlen: cache dtype %d / out dtype %d", cache_dtype, out_dtype); return; }
 #undef LAV_R
 #undef LAV
     count_launch();
     check_launch("latent_attention_varlen");
 }
 
-void latent_out_gate(const float* src, const void* w_uv, const float* gate, int64_t ld_gate, void* out, int32_t num_tokens, int32_t num_heads, int32_t dv,
-                     int32_t rank, int32_t w_dtype, int32_t out_dtype, int64_t stream) {
+void latent_out_gate(const float* src, int64_t src_stride_token, int64_t src_stride_head, const void* w_uv, const float* gate, int64_t ld_gate, void* out,
+                     int32_t num_tokens, int32_t num_heads, int32_t dv, int32_t rank, int32_t w_dtype, int32_t out_dtype, int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(src && out && num_heads > 0 && num_heads <= 65535 && dv > 0 && rank > 0 && rank <= 8192 && (!gate || ld_gate >= num_heads), kErrBadArg,
                  "latent_out_gate: bad arguments");
     cudaStream_t st = as_stream(stream);
     const size_t smem = (size_t)rank * sizeof(float);
     const dim3 grid(num_tokens, num_heads);
-#define LOG(TW, TO) launch_pdl(latent_out_gate_kernel<TW, TO>, grid, dim3(128), smem, st, src, (const TW*)w_uv, gate, ld_gate, (TO*)out, num_heads, dv, rank)
+#define LOG(TW, TO) launch_pdl(latent_out_gate_kernel<TW, TO>, grid, dim3(128), smem, st, src, src_stride_token, src_stride_head, (const TW*)w_uv, gate, ld_gate, (TO*)out, \
+                               num_heads, dv, rank)
     if (w_dtype == B200_F32 && out_dtype == B200_F32) LOG(float, float);
     else if (w_dtype == B200_BF16 && out_dtype == B200_BF16) LOG(__nv_bfloat16, __nv_bfloat16);
     else if (w_dtype == B200_BF16 && out_dtype == B200_F32) LOG(__nv_bfloat16, float);

@@ -10,6 +10,9 @@
 //                     experts (no weights) and are skipped.
 //   moe_down_combine  out[t] = sum over the token's choices, in choice order, of weight * (W_down[e] act[p]), or weight * x[t] for an
 //                     identity expert.
+// Steps with many rows (bf16): moe_align sorts the pairs by expert into tiles of 128 rows (padding each expert's run), moe_gather_rows copies
+// the tokens' rows into that order, the two expert products run as grouped tcgen05 GEMMs (dense_gemm.cu, the weight tile chosen per row tile),
+// silu_mul_packed sits between them, and moe_combine_rows adds each token's choices in choice order -- the same sum as moe_down_combine.
 #include "common.cuh"
 
 namespace b200 {
@@ -132,6 +135,80 @@ moe_down_combine_kernel(const T* __restrict__ act, const T* __restrict__ w_d, co
     }
 }
 
+constexpr int kTile = 128;
+
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ pair_row, int32_t* __restrict__ row_pair, int32_t* __restrict__ tile_group, int pairs,
+                 int E, int max_rows) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ int sh[];
+    int* count = sh;               // [E]
+    int* start = sh + E;           // [E + 1] first row of every expert's padded run
+    int* cursor = sh + 2 * E + 1;  // [E]
+    for (int e = threadIdx.x; e < E; e += 1024) { count[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += 1024) { const int e = ids[p]; if (e >= 0 && e < E) atomicAdd(&count[e], 1); }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) { start[e] = at; at += (count[e] + kTile - 1) / kTile * kTile; }
+        start[E] = at;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < max_rows; r += 1024) row_pair[r] = -1;
+    for (int i = threadIdx.x; i < max_rows / kTile; i += 1024) tile_group[i] = -1;
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += 1024)
+        for (int i = start[e] / kTile; i < start[e + 1] / kTile; ++i) tile_group[i] = e;
+    for (int p = threadIdx.x; p < pairs; p += 1024) {
+        const int e = ids[p];
+        int row = -1;
+        if (e >= 0 && e < E) { row = start[e] + atomicAdd(&cursor[e], 1); row_pair[row] = p; }
+        pair_row[p] = row;
+    }
+}
+
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, int64_t ldh, const int32_t* __restrict__ row_pair, __nv_bfloat16* __restrict__ xg, int top, int D) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t r = blockIdx.x;
+    const int p = row_pair[r];
+    __nv_bfloat16* dst = xg + r * D;
+    if (p < 0) { for (int i = threadIdx.x; i < D; i += 128) dst[i] = __float2bfloat16_rn(0.f); return; }
+    const __nv_bfloat16* src = h + (int64_t)(p / top) * ldh;
+    for (int i = threadIdx.x; i < D; i += 128) dst[i] = src[i];
+}
+
+template <typename TOut>
+__global__ void silu_mul_packed_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int64_t rows, int ff, int64_t ld) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * ff) return;
+    const int64_t r = i / ff;
+    const int c = (int)(i - r * ff);
+    const float g = gu[r * ld + c], u = gu[r * ld + ff + c];
+    out[i] = from_f32<TOut>(g / (1.0f + expf(-g)) * u);
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_rows_kernel(const float* __restrict__ y, const int32_t* __restrict__ pair_row, const float* __restrict__ weights, const float* __restrict__ x,
+                        int64_t ldx, float* __restrict__ out, int top, int D) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t t = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += 256) {
+        float tot = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int row = pair_row[t * top + k];
+            tot = fmaf(weights[t * top + k], row >= 0 ? y[(int64_t)row * D + d] : x[t * ldx + d], tot);
+        }
+        out[t * D + d] = tot;
+    }
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -190,6 +267,50 @@ void moe_down_combine(const void* act, const void* w_down, const int32_t* ids, c
     } else { set_error(kErrUnsupported, "moe_down_combine: dtype %d (f32 / bf16)", dtype); return; }
     count_launch();
     check_launch("moe_down_combine");
+}
+
+int64_t moe_align_rows(int64_t pairs, int32_t num_experts) {
+    // every expert's run is padded to whole tiles: at most kTile - 1 rows of padding each
+    return (pairs + (int64_t)num_experts * (kTile - 1) + kTile - 1) / kTile * kTile;
+}
+
+void moe_align(const int32_t* ids, int32_t* pair_row, int32_t* row_pair, int32_t* tile_group, int32_t pairs, int32_t num_experts, int32_t max_rows, int64_t stream) {
+    if (pairs == 0) return;
+    B200_REQUIRE(ids && pair_row && row_pair && tile_group && pairs > 0 && num_experts > 0 && num_experts <= 4096 && max_rows % kTile == 0 &&
+                 max_rows >= moe_align_rows(pairs, num_experts), kErrBadArg, "moe_align: bad arguments");
+    launch_pdl(moe_align_kernel, dim3(1), dim3(1024), (size_t)(3 * num_experts + 1) * sizeof(int), as_stream(stream), ids, pair_row, row_pair, tile_group, pairs,
+               num_experts, max_rows);
+    count_launch();
+    check_launch("moe_align");
+}
+
+void moe_gather_rows(const void* h, int64_t ldh, const int32_t* row_pair, void* xg, int32_t max_rows, int32_t top, int32_t width, int64_t stream) {
+    if (max_rows == 0) return;
+    B200_REQUIRE(h && row_pair && xg && top > 0 && width > 0 && ldh >= width, kErrBadArg, "moe_gather_rows: bad arguments");
+    launch_pdl(moe_gather_rows_kernel, dim3(max_rows), dim3(128), 0, as_stream(stream), (const __nv_bfloat16*)h, ldh, row_pair, (__nv_bfloat16*)xg, top, width);
+    count_launch();
+    check_launch("moe_gather_rows");
+}
+
+void silu_mul_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, int64_t ld, int32_t out_dtype, int64_t stream) {
+    if (rows == 0 || ff == 0) return;
+    B200_REQUIRE(gate_up && out && rows > 0 && ff > 0 && ld >= 2 * (int64_t)ff, kErrBadArg, "silu_mul_packed: bad arguments");
+    const unsigned grid = (unsigned)((rows * ff + 255) / 256);
+    cudaStream_t st = as_stream(stream);
+    if (out_dtype == B200_F32) launch_pdl(silu_mul_packed_kernel<float>, dim3(grid), dim3(256), 0, st, gate_up, (float*)out, rows, ff, ld);
+    else if (out_dtype == B200_BF16) launch_pdl(silu_mul_packed_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, gate_up, (__nv_bfloat16*)out, rows, ff, ld);
+    else { set_error(kErrUnsupported, "silu_mul_packed: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    check_launch("silu_mul_packed");
+}
+
+void moe_combine_rows(const float* y, const int32_t* pair_row, const float* weights, const float* x, int64_t ldx, float* out, int32_t num_tokens, int32_t top,
+                      int32_t width, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(y && pair_row && weights && x && out && top > 0 && width > 0 && ldx >= width, kErrBadArg, "moe_combine_rows: bad arguments");
+    launch_pdl(moe_combine_rows_kernel, dim3(num_tokens), dim3(256), 0, as_stream(stream), y, pair_row, weights, x, ldx, out, top, width);
+    count_launch();
+    check_launch("moe_combine_rows");
 }
 
 }  // extern "C"

@@ -142,6 +142,9 @@ class GatedMlp:
         return ops.linear(ops.gelu_tanh_mul(ops.linear(h, self.w_in), self.dtype), self.w_down)
 
 
+GROUPED_MIN_ROWS = 256        # rows (tokens, or token-choice pairs) from which the grouped tensor-core products replace the streaming kernels
+
+
 class LatentAttentionMixer:
     """Multi-head attention over a low-rank latent: per token the cache holds the normed latent c [rank] and one rotated key part [rot_dim] shared by
     all heads; head h's key is (W_uk[h] c | rotated part), its value W_uv[h] c; the softmax denominator may hold a per-head sink, the head outputs
@@ -180,6 +183,11 @@ class LatentAttentionMixer:
         self.w_uk = w["uk"].to(dtype).contiguous()
         self.w_uv = w["uv"].to(dtype).contiguous()
         self.w_o = w["o"].to(dtype).contiguous()
+        # steps with many rows (bf16, TMA-sized operands): both up-projections run head by head as ONE grouped product on the tensor-core GEMM;
+        # its weight operand is [n, k] per head: W_uk[h]^T [rank, dn] and W_uv[h] [dv, rank]
+        self.grouped = dtype == torch.bfloat16 and dn % 8 == 0 and rank % 8 == 0 and dn >= 64 and rank >= 64
+        self.uk_t = self.w_uk.view(heads, dn, rank).transpose(1, 2).contiguous() if self.grouped else None
+        self._tile_heads = {}
         self.cos = self.sin = None
         self._device = self.w_in.device
         if rot and rot_dim:
@@ -199,9 +207,31 @@ class LatentAttentionMixer:
         proj = ops.linear(h, self.w_in)
         if not self.shared:
             ops.latent_kv_rope_cache(proj, self.off_dkv, self.c_norm, self.cos, self.sin, batch, c_cache, kr_cache, self.R, self.dr, self.eps)
-        q_lat = ops.latent_q_absorb(proj, self.w_uk, self.cos, self.sin, batch, self.H, self.dn, self.dr, self.R)
-        o_lat = ops.latent_attention_varlen(q_lat, c_cache, kr_cache, batch, self.sink, self.H, self.R, self.dr, self.block_size, self.scale, self.window)
-        a = ops.latent_out_gate(o_lat, self.w_uv, proj[:, self.off_g:] if self.has_gate else None, self.H, self.dv, self.R, self.dtype)
+        gate = proj[:, self.off_g:] if self.has_gate else None
+        T = proj.shape[0]
+        if self.grouped and T >= GROUPED_MIN_ROWS:
+            # head-major buffers, every head's rows padded to whole 128-row tiles; tile i belongs to head i // (tiles per head)
+            Tp = -(-T // 128) * 128
+            if Tp not in self._tile_heads:
+                self._tile_heads[Tp] = (torch.arange(self.H * Tp // 128, dtype=torch.int32, device=proj.device) // (Tp // 128)).to(torch.int32)
+            heads_of = self._tile_heads[Tp]
+            qn16 = torch.zeros((self.H, Tp, self.dn), dtype=torch.bfloat16, device=proj.device) if Tp != T else torch.empty((self.H, Tp, self.dn), dtype=torch.bfloat16,
+                                                                                                                         device=proj.device)
+            q_hm = torch.empty((self.H, Tp, self.R + self.dr), dtype=torch.float32, device=proj.device)
+            q_lat = q_hm.transpose(0, 1)                                     # [Tp, H, R + dr] view: token stride R + dr, head stride Tp (R + dr)
+            ops.latent_q_absorb(proj, None, self.cos, self.sin, batch, self.H, self.dn, self.dr, self.R, q_lat=q_lat, qn16=qn16)
+            ops.linear_grouped(qn16.view(self.H * Tp, self.dn), self.uk_t, heads_of, q_hm.view(self.H * Tp, self.R + self.dr))
+            o16 = torch.zeros((self.H, Tp, self.R), dtype=torch.bfloat16, device=proj.device) if Tp != T else torch.empty((self.H, Tp, self.R), dtype=torch.bfloat16,
+                                                                                                                       device=proj.device)
+            ops.latent_attention_varlen(q_lat[:T], c_cache, kr_cache, batch, self.sink, self.H, self.R, self.dr, self.block_size, self.scale, self.window,
+                                        out=o16.transpose(0, 1)[:T])
+            v_hm = torch.empty((self.H, Tp, self.dv), dtype=torch.float32, device=proj.device)
+            ops.linear_grouped(o16.view(self.H * Tp, self.R), self.w_uv.view(self.H, self.dv, self.R), heads_of, v_hm.view(self.H * Tp, self.dv))
+            a = ops.latent_out_gate(v_hm.transpose(0, 1)[:T], None, gate, self.H, self.dv, self.R, self.dtype)
+        else:
+            q_lat = ops.latent_q_absorb(proj, self.w_uk, self.cos, self.sin, batch, self.H, self.dn, self.dr, self.R)
+            o_lat = ops.latent_attention_varlen(q_lat, c_cache, kr_cache, batch, self.sink, self.H, self.R, self.dr, self.block_size, self.scale, self.window)
+            a = ops.latent_out_gate(o_lat, self.w_uv, gate, self.H, self.dv, self.R, self.dtype)
         return ops.linear(a, self.w_o)
 
 
@@ -226,10 +256,20 @@ class RoutedExperts:
             self.w_gu = torch.stack([torch.cat([w[f"e{j}.gate"], w[f"e{j}.up"]], 0) for j in range(experts)], 0).to(dtype).contiguous()
             self.w_d = torch.stack([w[f"e{j}.down"] for j in range(experts)], 0).to(dtype).contiguous()
             self.ff = self.w_d.shape[2]
+        D = self.router.shape[1]
+        # steps with many rows (bf16, TMA-sized operands): pairs sorted by expert, both expert products as grouped products on the tensor-core GEMM
+        self.grouped = bool(experts) and dtype == torch.bfloat16 and D % 8 == 0 and self.ff % 8 == 0 and D >= 64 and self.ff >= 64
 
     def forward(self, h: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         """h: the input in the compute dtype, x: the same rows in f32 (what an identity expert returns)"""
         ids, wts = ops.moe_route(ops.linear(h, self.router), self.correction, self.top, self.groups, self.keep, self.scale)
+        if self.grouped and h.shape[0] * self.top >= GROUPED_MIN_ROWS:
+            pair_row, row_pair, tile_expert = ops.moe_sorted_rows(ids, self.E)
+            xg = ops.moe_gather_rows(h, row_pair, self.top)
+            gu = ops.linear_grouped(xg, self.w_gu, tile_expert, torch.empty((xg.shape[0], 2 * self.ff), dtype=torch.float32, device=h.device))
+            act = ops.silu_mul_packed(gu, torch.bfloat16)
+            y = ops.linear_grouped(act, self.w_d, tile_expert, torch.empty((xg.shape[0], self.w_d.shape[1]), dtype=torch.float32, device=h.device))
+            return ops.moe_combine_rows(y, pair_row, wts, x)
         act = ops.moe_gate_up(h, self.w_gu, ids) if self.E else None
         return ops.moe_down_combine(act, self.w_d, ids, wts, x, self.E, self.ff)
 

@@ -278,39 +278,65 @@ def latent_kv_rope_cache(proj: torch.Tensor, off: int, norm_w: Optional[torch.Te
 
 
 def latent_q_absorb(proj: torch.Tensor, w_uk: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], batch: StepBatch, heads: int,
-                    dn: int, rot_dim: int, rank: int, q_lat: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """-> q_lat f32 [T, H, rank + rot_dim]; w_uk None writes only the rotated part (the caller fills [..., :rank])"""
+                    dn: int, rot_dim: int, rank: int, q_lat: Optional[torch.Tensor] = None, qn16: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """-> q_lat f32 [T, H, rank + rot_dim] (or the given tensor of any token / head strides whose last axis is contiguous); w_uk None writes only
+    the rotated part (the caller fills [..., :rank]); ``qn16`` bf16 [H, rows, dn] also receives the unrotated part, head by head."""
     T = proj.shape[0]
     if cos is not None and batch.max_position >= cos.shape[0]:
         raise BackendError(f"position {batch.max_position} is outside the rotary table ({cos.shape[0]} rows)")
     if q_lat is None:
         q_lat = torch.empty((T, heads, rank + rot_dim), dtype=torch.float32, device=proj.device)
+    if q_lat.stride(2) != 1 or q_lat.dtype != torch.float32 or (qn16 is not None and (qn16.dtype != torch.bfloat16 or not qn16.is_contiguous())):
+        raise BackendError("latent_q_absorb: q_lat is f32 with a contiguous last axis, qn16 contiguous bf16")
     lib().latent_q_absorb(_ptr(proj), C.c_int64(proj.stride(0) if T > 1 else proj.shape[1]), _ptr(w_uk), _ptr(cos), _ptr(sin), C.c_int32(0 if cos is None else cos.shape[0]),
-                          _ptr(batch.positions), _ptr(q_lat), C.c_int32(T), C.c_int32(heads), C.c_int32(dn), C.c_int32(rot_dim), C.c_int32(rank),
+                          _ptr(batch.positions), _ptr(q_lat), C.c_int64(q_lat.stride(0)), C.c_int64(q_lat.stride(1)), _ptr(qn16),
+                          C.c_int64(0 if qn16 is None else qn16.shape[1]), C.c_int32(T), C.c_int32(heads), C.c_int32(dn), C.c_int32(rot_dim), C.c_int32(rank),
                           C.c_int32(_tag(w_uk.dtype) if w_uk is not None else DType.F32), _stream(proj.device))
     check("latent_q_absorb")
     return q_lat
 
 
 def latent_attention_varlen(q_lat: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor, batch: StepBatch, sink: Optional[torch.Tensor], heads: int,
-                            rank: int, rot_dim: int, block_size: int, scale: float, window: int = 0) -> torch.Tensor:
+                            rank: int, rot_dim: int, block_size: int, scale: float, window: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q_lat f32 [T, H, rank + rot_dim] (any token / head strides) -> o f32 [T, H, rank], or into ``out`` (f32 or bf16, any token / head strides)"""
     T = q_lat.shape[0]
-    o = torch.empty((T, heads, rank), dtype=torch.float32, device=q_lat.device)
-    lib().latent_attention_varlen(_ptr(o), _ptr(q_lat), _ptr(c_cache), _ptr(kr_cache), _ptr(batch.block_tables), C.c_int32(batch.block_tables.shape[1]),
+    if out is None:
+        out = torch.empty((T, heads, rank), dtype=torch.float32, device=q_lat.device)
+    if q_lat.stride(2) != 1 or out.stride(2) != 1:
+        raise BackendError("latent_attention_varlen: the last axis of q_lat and out is contiguous")
+    lib().latent_attention_varlen(_ptr(out), C.c_int64(out.stride(0)), C.c_int64(out.stride(1)), C.c_int32(_tag(out.dtype)), _ptr(q_lat), C.c_int64(q_lat.stride(0)),
+                                  C.c_int64(q_lat.stride(1)), _ptr(c_cache), _ptr(kr_cache), _ptr(batch.block_tables), C.c_int32(batch.block_tables.shape[1]),
                                   _ptr(batch.token_seq), _ptr(batch.positions), _ptr(sink), C.c_int32(T), C.c_int32(heads), C.c_int32(rank), C.c_int32(rot_dim),
                                   C.c_int32(block_size), C.c_float(scale), C.c_int32(window), C.c_int32(_tag(c_cache.dtype)), _stream(q_lat.device))
     check("latent_attention_varlen")
-    return o
+    return out
 
 
 def latent_out_gate(src: torch.Tensor, w_uv: Optional[torch.Tensor], gate: Optional[torch.Tensor], heads: int, dv: int, rank: int, out_dtype: torch.dtype) -> torch.Tensor:
-    """sigmoid(gate[t, h]) * (w_uv[h] src[t, h]) -> [T, H dv]; w_uv None: src is [T, H, dv] already"""
+    """sigmoid(gate[t, h]) * (w_uv[h] src[t, h]) -> [T, H dv]; src f32 [T, H, rank] of any token / head strides; w_uv None: src is [T, H, dv] already"""
     T = src.shape[0]
     out = torch.empty((T, heads * dv), dtype=out_dtype, device=src.device)
-    lib().latent_out_gate(_ptr(src), _ptr(w_uv), _ptr(gate), C.c_int64(0 if gate is None else (gate.stride(0) if T > 1 else max(heads, gate.stride(0)))), _ptr(out),
+    if src.dtype != torch.float32 or src.stride(2) != 1:
+        raise BackendError("latent_out_gate: src is f32 with a contiguous last axis")
+    lib().latent_out_gate(_ptr(src), C.c_int64(src.stride(0)), C.c_int64(src.stride(1)), _ptr(w_uv), _ptr(gate),
+                          C.c_int64(0 if gate is None else (gate.stride(0) if T > 1 else max(heads, gate.stride(0)))), _ptr(out),
                           C.c_int32(T), C.c_int32(heads), C.c_int32(dv), C.c_int32(rank), C.c_int32(_tag(w_uv.dtype) if w_uv is not None else _tag(out_dtype)),
                           C.c_int32(_tag(out_dtype)), _stream(src.device))
     check("latent_out_gate")
+    return out
+
+
+def linear_grouped(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r, :n] = x[r] . weight[tile_group[r // 128]]^T on the tcgen05 GEMM: x bf16 [m_pad, k] (m_pad % 128 == 0, rows may be strided), weight bf16
+    [groups, n, k], tile_group i32 [m_pad / 128] (negative = skip the tile), out f32 or bf16 [m_pad, >= n] (rows may be strided)."""
+    m, k = x.shape
+    G, n, _ = weight.shape
+    if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not weight.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1 or m % 128 or
+            tile_group.dtype != torch.int32 or tile_group.numel() < m // 128 or weight.shape[2] != k or out.shape[0] != m or out.shape[1] < n):
+        raise BackendError(f"linear_grouped: x {tuple(x.shape)} {x.dtype}, weight {tuple(weight.shape)} {weight.dtype}, out {tuple(out.shape)}")
+    lib().linear_grouped(_ptr(x), _ptr(weight), _ptr(out), _ptr(tile_group), C.c_int32(m), C.c_int32(n), C.c_int32(k), C.c_int32(G), C.c_int64(x.stride(0)),
+                         C.c_int64(out.stride(0)), C.c_int32(_tag(out.dtype)), _stream(x.device))
+    check("linear_grouped")
     return out
 
 
@@ -347,4 +373,43 @@ def moe_down_combine(act: Optional[torch.Tensor], w_down: Optional[torch.Tensor]
     lib().moe_down_combine(_ptr(act), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(x), C.c_int64(x.stride(0) if T > 1 else max(D, x.stride(0))), _ptr(out), C.c_int32(T),
                            C.c_int32(top), C.c_int32(num_experts), C.c_int32(ff), C.c_int32(D), C.c_int32(dt), _stream(x.device))
     check("moe_down_combine")
+    return out
+
+
+def moe_sorted_rows(ids: torch.Tensor, num_experts: int):
+    """pairs (token, choice) sorted by expert into tiles of 128 rows -> (pair_row i32 [T * top] (-1 for identity choices), row_pair i32 [rows] (-1 =
+    padding), tile_group i32 [rows / 128] (-1 = unused tile)); rows = an upper bound that depends on the counts only through their number"""
+    P = ids.numel()
+    rows = int(lib().moe_align_rows(C.c_int64(P), C.c_int32(num_experts)))
+    pair_row = torch.empty((P,), dtype=torch.int32, device=ids.device)
+    row_pair = torch.empty((rows,), dtype=torch.int32, device=ids.device)
+    tile_group = torch.empty((rows // 128,), dtype=torch.int32, device=ids.device)
+    lib().moe_align(_ptr(ids), _ptr(pair_row), _ptr(row_pair), _ptr(tile_group), C.c_int32(P), C.c_int32(num_experts), C.c_int32(rows), _stream(ids.device))
+    check("moe_align")
+    return pair_row, row_pair, tile_group
+
+
+def moe_gather_rows(h: torch.Tensor, row_pair: torch.Tensor, top: int) -> torch.Tensor:
+    rows, D = row_pair.shape[0], h.shape[1]
+    xg = torch.empty((rows, D), dtype=torch.bfloat16, device=h.device)
+    lib().moe_gather_rows(_ptr(h), C.c_int64(h.stride(0)), _ptr(row_pair), _ptr(xg), C.c_int32(rows), C.c_int32(top), C.c_int32(D), _stream(h.device))
+    check("moe_gather_rows")
+    return xg
+
+
+def silu_mul_packed(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    rows, two_ff = gate_up.shape
+    out = torch.empty((rows, two_ff // 2), dtype=out_dtype, device=gate_up.device)
+    lib().silu_mul_packed(_ptr(gate_up), _ptr(out), C.c_int64(rows), C.c_int32(two_ff // 2), C.c_int64(gate_up.stride(0)), C.c_int32(_tag(out_dtype)), _stream(gate_up.device))
+    check("silu_mul_packed")
+    return out
+
+
+def moe_combine_rows(y: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    T, D = x.shape
+    top = weights.shape[1]
+    out = torch.empty((T, D), dtype=torch.float32, device=x.device)
+    lib().moe_combine_rows(_ptr(y), _ptr(pair_row), _ptr(weights), _ptr(x), C.c_int64(x.stride(0) if T > 1 else max(D, x.stride(0))), _ptr(out), C.c_int32(T),
+                           C.c_int32(top), C.c_int32(D), _stream(x.device))
+    check("moe_combine_rows")
     return out

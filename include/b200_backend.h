@@ -509,12 +509,31 @@ void latent_kv_rope_cache(const float* proj, int64_t ld, int32_t off, const floa
                           const int32_t* positions, const int64_t* slot_mapping, void* c_cache, void* kr_cache, int32_t num_tokens, int32_t rank,
                           int32_t rot_dim, float eps, int32_t cache_dtype, int64_t stream);
 void latent_q_absorb(const float* proj, int64_t ld, const void* w_uk, const float* cos_t, const float* sin_t, int32_t max_pos, const int32_t* positions,
-                     float* q_lat, int32_t num_tokens, int32_t num_heads, int32_t dn, int32_t rot_dim, int32_t rank, int32_t w_dtype, int64_t stream);
-void latent_attention_varlen(float* o_lat, const float* q_lat, const void* c_cache, const void* kr_cache, const int32_t* block_tables, int32_t table_width,
+                     float* q_lat, int64_t q_stride_token, int64_t q_stride_head, void* qn16, int64_t rows16, int32_t num_tokens, int32_t num_heads, int32_t dn,
+                     int32_t rot_dim, int32_t rank, int32_t w_dtype, int64_t stream);
+void latent_attention_varlen(void* o_lat, int64_t o_stride_token, int64_t o_stride_head, int32_t out_dtype, const float* q_lat, int64_t q_stride_token,
+                             int64_t q_stride_head, const void* c_cache, const void* kr_cache, const int32_t* block_tables, int32_t table_width,
                              const int32_t* token_seq, const int32_t* positions, const float* sink, int32_t num_tokens, int32_t num_heads, int32_t rank,
                              int32_t rot_dim, int32_t block_size, float scale, int32_t window, int32_t cache_dtype, int64_t stream);
-void latent_out_gate(const float* src, const void* w_uv, const float* gate, int64_t ld_gate, void* out, int32_t num_tokens, int32_t num_heads, int32_t dv,
-                     int32_t rank, int32_t w_dtype, int32_t out_dtype, int64_t stream);
+void latent_out_gate(const float* src, int64_t src_stride_token, int64_t src_stride_head, const void* w_uv, const float* gate, int64_t ld_gate, void* out,
+                     int32_t num_tokens, int32_t num_heads, int32_t dv, int32_t rank, int32_t w_dtype, int32_t out_dtype, int64_t stream);
+/* linear_grouped: out[r, :n] (out_dtype F32 / BF16, row pitch ldy) = x[r, :k] . weight[tile_group[r / 128]]^T: bf16 x [m_pad, k] (row pitch ldx, m_pad a
+ *   multiple of 128) whose rows come in tiles of 128 that each multiply one matrix of the bf16 stack weight [groups, n, k]; tile_group i32 [m_pad / 128] on
+ *   the device, a negative entry skips the tile.  The tcgen05 GEMM of linear_16bit with the weight tile chosen per row tile.
+ * moe_align: pairs (token, choice) sorted by expert into tiles of 128 rows: ids i32 [pairs]; pair_row[p] = its row in the sorted, padded order (-1 for an
+ *   identity choice, id >= num_experts), row_pair i32 [max_rows] the inverse (-1 = padding), tile_group i32 [max_rows / 128] the expert of every tile (-1 =
+ *   unused); max_rows >= moe_align_rows(pairs, num_experts).
+ * moe_gather_rows: xg bf16 [max_rows, width] = h[row_pair[r] / top] (zeros for padding).
+ * silu_mul_packed: out[r, :ff] = silu(gu[r, :ff]) * gu[r, ff : 2 ff] from f32 gu, out_dtype F32 / BF16.
+ * moe_combine_rows: out f32 [T, width] = sum_k weights[t, k] * (pair_row >= 0 ? y[pair_row[t, k]] : x[t]), in choice order. */
+void linear_grouped(const void* x, const void* weight, void* out, const int32_t* tile_group, int32_t m_pad, int32_t n, int32_t k, int32_t groups, int64_t ldx,
+                    int64_t ldy, int32_t out_dtype, int64_t stream);
+int64_t moe_align_rows(int64_t pairs, int32_t num_experts);
+void moe_align(const int32_t* ids, int32_t* pair_row, int32_t* row_pair, int32_t* tile_group, int32_t pairs, int32_t num_experts, int32_t max_rows, int64_t stream);
+void moe_gather_rows(const void* h, int64_t ldh, const int32_t* row_pair, void* xg, int32_t max_rows, int32_t top, int32_t width, int64_t stream);
+void silu_mul_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, int64_t ld, int32_t out_dtype, int64_t stream);
+void moe_combine_rows(const float* y, const int32_t* pair_row, const float* weights, const float* x, int64_t ldx, float* out, int32_t num_tokens, int32_t top,
+                      int32_t width, int64_t stream);
 void moe_route(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* weights, int32_t num_tokens, int32_t num_outputs, int32_t top,
                int32_t groups, int32_t keep, float scale, int64_t stream);
 void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, void* act, int32_t num_tokens, int32_t top, int32_t num_experts,

@@ -167,6 +167,45 @@ def test_routed_experts(E, I, top, ff, D, groups, dtype, tol):
     close(mlp.forward(dev(x, dtype), dev(x)), G.moe(x.to(F64), w, cfg["layers"][0]["mlp"]), tol, "routed experts")
 
 
+@pytest.mark.parametrize("n,k,G", [(64, 64, 3), (40, 72, 5), (300, 128, 2), (24, 200, 4)])
+def test_grouped_product_on_the_tensor_core_gemm(n, k, G):
+    """rows in tiles of 128, every tile multiplying the matrix its entry names (in any order, with skipped tiles), against float64 on the
+    same bf16 operands; rows of skipped tiles stay as they were"""
+    g = torch.Generator().manual_seed(n + k)
+    tiles = [1, -1, 0, G - 1, 1, -1, 0]
+    m = 128 * len(tiles)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(G, n, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    for dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 6e-3)):
+        out = torch.full((m, n + 8), 3.0, dtype=dt, device=DEV)
+        ops.linear_grouped(x.to(DEV), w.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV), out)
+        for i, e in enumerate(tiles):
+            rows = slice(128 * i, 128 * i + 128)
+            if e < 0:
+                assert float((out[rows].float() - 3.0).abs().max()) == 0.0
+            else:
+                close(out[rows, :n], x[rows].to(F64) @ w[e].to(F64).T, tol, f"tile {i} -> matrix {e}")
+                assert float((out[rows, n:].float() - 3.0).abs().max()) == 0.0
+
+
+def test_pairs_sorted_by_expert():
+    g = torch.Generator().manual_seed(0)
+    E, T, top = 5, 333, 3
+    ids = torch.randint(0, E + 2, (T, top), generator=g).to(torch.int32)           # ids E, E + 1 are identity choices
+    ids[ids == 3] = 4                                                              # an expert nobody chose
+    pair_row, row_pair, tile_group = (t.cpu() for t in ops.moe_sorted_rows(ids.to(DEV), E))
+    flat = ids.reshape(-1)
+    assert row_pair.shape[0] % 128 == 0 and tile_group.shape[0] == row_pair.shape[0] // 128
+    for p in range(T * top):
+        r = int(pair_row[p])
+        if flat[p] >= E:
+            assert r == -1
+        else:
+            assert int(row_pair[r]) == p and int(tile_group[r // 128]) == int(flat[p])
+    assert int((row_pair >= 0).sum()) == int((flat < E).sum())
+    assert 3 not in tile_group.tolist()
+
+
 def _mixer_case(H, dn, dr, dv, R, D, scaling, seed=0, **kw):
     cfg = S.guvusun_config(D, 30, [S.guvusun_layer(H, dn, dr, dv, R, scaling=scaling, **kw)])
     w = {k[len("l0.mix."):]: v for k, v in S.guvusun_weights(cfg, seed).items() if k.startswith("l0.mix.")}
@@ -425,7 +464,7 @@ def test_many_rows_take_the_tensor_core_routes():
     """a bf16 step with hundreds of rows and 8-aligned sizes: the expert products and the latent up-projections run as grouped products on
     the tensor-core GEMM; the same rows in steps of a few tokens run on the streaming kernels; both stay within rounding of the oracle and
     of each other"""
-    cfg = S.guvusun_config(128, 200, [S.guvusun_layer(4, 32, 16, 32, 64, experts=6, ff=64, top=2, identity=2, groups=(2, 1), router_scale=2.0, scaling=YARN),
+    cfg = S.guvusun_config(128, 200, [S.guvusun_layer(4, 64, 16, 32, 64, experts=6, ff=64, top=2, identity=2, groups=(2, 1), router_scale=2.0, scaling=YARN),
                                       S.guvusun_layer(8, 16, 16, 24, 64, experts=3, ff=128, top=2, kv_from=0, scaling=YARN)],
                            bigram=dict(buckets=101, mul_prev=11, mul_cur=3), side_dim=8)
     w = S.guvusun_weights(cfg, 2)
