@@ -49,7 +49,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--parity-steps", type=int, default=3, help="decode steps compared against a TP=1 engine before timing (0 = off)")
-    ap.add_argument("--arch", default="llama", choices=["llama", "gobesun"],
+    ap.add_argument("--arch", default="llama", choices=["llama", "gobesun", "guvusun"],
                     help="llama = the metric (default, unchanged).  gobesun = prefill / decode throughput of the Gobesun decoder at layer sizes of real "
                          "models (random weights), beside a dense bf16 Llama of equal width / heads / ff / depth, with a per-kernel roofline table; "
                          "one JSON line, single GPU.")
@@ -630,6 +630,74 @@ ARCH_SIZES = {
 }
 
 
+def llama_beside(pkg, S, BK, z, hd, P, B, CTX, K, W, blocks_per, toks, timed, dev):
+    """The dense bf16 Llama of the given width / heads / ff / depth: (prefill seconds per P-token prompt, decode seconds per step of B tokens at
+    context CTX, per-kernel prefill times).  Decode runs on its C++ engine; prefill is the same layer written with the framework's operators."""
+    import torch
+    from candle_vllm_b200.inputs import prepare_prompt, to_device
+    bf = torch.bfloat16
+    D, H, G, ff, V, NL = z["width"], z["heads"], z["kv"], z["ff"], z["vocab"], z["layers"]
+    # ---- Llama of equal size ---------------------------------------------------------------------------------------------------
+    lcfg = pkg.LlamaConfig(hidden=D, num_layers=NL, num_heads=H, num_kv_heads=G, head_dim=hd, ffn=ff, vocab=V, rms_eps=1e-5, rope_theta=1e6,
+                           max_pos=P + 64, block_size=64, max_num_seqs=B, max_blocks_per_seq=blocks_per)
+    lw = S.make_weights_16bit(lcfg, dev, seed=0, dtype=bf)
+    nblk = max(B * blocks_per, P // 64 + 1)
+    eng = pkg.CacheEngine(NL, G, hd, pkg.CacheConfig(64, nblk), device=dev)
+    S.fill_kv_cache(eng.gpu_cache, seed=1)
+    lm = pkg.GGUFLLaMa(lcfg, lw, eng.gpu_cache, kv_dtype=pkg.DType.BF16, rope_neox=True)
+    tables = S.random_block_tables(B, blocks_per, nblk, seed=2)
+    prep = pkg.prepare_decode([CTX + 1] * B, toks[:B], tables, 64)
+    lm.decode(prep)
+    l_dec = timed(lambda: lm.decode_resident(B, advance=True), K, W)
+    # prefill: the same layer written with the framework's operators (the decode engine has no prompt path of its own)
+    lk = {}
+    pp = prepare_prompt([toks], [list(range(P // 64 + 1))], 64)
+    tok_d, pos_d, meta = to_device(pp, dev)
+    inv = 1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+    ang = torch.arange(P + 64, dtype=torch.float64)[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+    att = BK.PagedAttention(H, hd, hd ** -0.5, G)
+    lin = {k: [BK.Linear(l[k]) for l in lw["layers"]] for k in ("wq", "wk", "wv", "wo", "w1", "w2", "w3")}
+    lin_out = BK.Linear(lw["output"])
+    emb = lw["tok_embeddings"]
+
+    def op(key, fn, rec):
+        if not rec:
+            return fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(); e0.record()
+        r = fn()
+        e1.record(); torch.cuda.synchronize()
+        lk.setdefault(key, []).append(e0.elapsed_time(e1) * 1e-3)
+        return r
+
+    def l_prefill(rec=False):
+        x = emb[tok_d]
+        for i, l in enumerate(lw["layers"]):
+            h = op("rms_norm", lambda: BK.rms_norm(x, l["attn_norm"], 1e-5, bf), rec)
+            q = op(f"linear[{H * hd}x{D}]", lambda: lin["wq"][i].forward(h), rec)
+            k = lin["wk"][i].forward(h); v = lin["wv"][i].forward(h)
+            qf, kf = q.float().view(P, H, hd), k.float().view(P, G, hd)
+            op("fused_rope", lambda: BK.fused_rope(qf, kf, cos, sin, pos_d, False), rec)
+            kc, vc = eng.gpu_cache[i]
+            qb, kb = qf.to(bf), kf.to(bf)
+            op("reshape_and_cache", lambda: BK.reshape_and_cache(kb, v.view(P, G, hd), kc, vc, meta.slot_mapping), rec)
+            a = op("paged_attention_prefill", lambda: att.forward(qb, None, None, None, kc, vc, meta), rec)
+            x = x + lin["wo"][i].forward(a.view(P, H * hd)).float()
+            h = BK.rms_norm(x, l["ffn_norm"], 1e-5, bf)
+            g1 = op(f"linear[{ff}x{D}]", lambda: lin["w1"][i].forward(h), rec)
+            u = lin["w3"][i].forward(h)
+            m = op("silu_mul", lambda: BK.silu_mul(g1.float(), u.float(), torch.float32), rec).to(bf)
+            x = x + op(f"linear[{D}x{ff}]", lambda: lin["w2"][i].forward(m), rec).float()
+        return lin_out.forward(BK.rms_norm(x[-1:], lw["norm"], 1e-5, bf))
+    l_pre = timed(l_prefill, 3, 2)
+    l_prefill(True); lk.clear(); l_prefill(True)
+    del lm, eng, lw, lin, lin_out
+    torch.cuda.empty_cache()
+
+    return l_pre, l_dec, lk
+
+
 def run_gobesun(args):
     import torch
     import candle_vllm_b200 as pkg
@@ -721,64 +789,7 @@ def run_gobesun(args):
         del runner, model
         torch.cuda.empty_cache()
 
-        # ---- Llama of equal size ---------------------------------------------------------------------------------------------------
-        lcfg = pkg.LlamaConfig(hidden=D, num_layers=NL, num_heads=H, num_kv_heads=G, head_dim=hd, ffn=ff, vocab=V, rms_eps=1e-5, rope_theta=1e6,
-                               max_pos=P + 64, block_size=64, max_num_seqs=B, max_blocks_per_seq=blocks_per)
-        lw = S.make_weights_16bit(lcfg, dev, seed=0, dtype=bf)
-        nblk = max(B * blocks_per, P // 64 + 1)
-        eng = pkg.CacheEngine(NL, G, hd, pkg.CacheConfig(64, nblk), device=dev)
-        S.fill_kv_cache(eng.gpu_cache, seed=1)
-        lm = pkg.GGUFLLaMa(lcfg, lw, eng.gpu_cache, kv_dtype=pkg.DType.BF16, rope_neox=True)
-        tables = S.random_block_tables(B, blocks_per, nblk, seed=2)
-        prep = pkg.prepare_decode([CTX + 1] * B, toks[:B], tables, 64)
-        lm.decode(prep)
-        l_dec = timed(lambda: lm.decode_resident(B, advance=True), K, W)
-        # prefill: the same layer written with the framework's operators (the decode engine has no prompt path of its own)
-        lk = {}
-        pp = prepare_prompt([toks], [list(range(P // 64 + 1))], 64)
-        tok_d, pos_d, meta = to_device(pp, dev)
-        inv = 1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
-        ang = torch.arange(P + 64, dtype=torch.float64)[:, None] * inv[None, :]
-        cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
-        att = BK.PagedAttention(H, hd, hd ** -0.5, G)
-        lin = {k: [BK.Linear(l[k]) for l in lw["layers"]] for k in ("wq", "wk", "wv", "wo", "w1", "w2", "w3")}
-        lin_out = BK.Linear(lw["output"])
-        emb = lw["tok_embeddings"]
-
-        def op(key, fn, rec):
-            if not rec:
-                return fn()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize(); e0.record()
-            r = fn()
-            e1.record(); torch.cuda.synchronize()
-            lk.setdefault(key, []).append(e0.elapsed_time(e1) * 1e-3)
-            return r
-
-        def l_prefill(rec=False):
-            x = emb[tok_d]
-            for i, l in enumerate(lw["layers"]):
-                h = op("rms_norm", lambda: BK.rms_norm(x, l["attn_norm"], 1e-5, bf), rec)
-                q = op(f"linear[{H * hd}x{D}]", lambda: lin["wq"][i].forward(h), rec)
-                k = lin["wk"][i].forward(h); v = lin["wv"][i].forward(h)
-                qf, kf = q.float().view(P, H, hd), k.float().view(P, G, hd)
-                op("fused_rope", lambda: BK.fused_rope(qf, kf, cos, sin, pos_d, False), rec)
-                kc, vc = eng.gpu_cache[i]
-                qb, kb = qf.to(bf), kf.to(bf)
-                op("reshape_and_cache", lambda: BK.reshape_and_cache(kb, v.view(P, G, hd), kc, vc, meta.slot_mapping), rec)
-                a = op("paged_attention_prefill", lambda: att.forward(qb, None, None, None, kc, vc, meta), rec)
-                x = x + lin["wo"][i].forward(a.view(P, H * hd)).float()
-                h = BK.rms_norm(x, l["ffn_norm"], 1e-5, bf)
-                g1 = op(f"linear[{ff}x{D}]", lambda: lin["w1"][i].forward(h), rec)
-                u = lin["w3"][i].forward(h)
-                m = op("silu_mul", lambda: BK.silu_mul(g1.float(), u.float(), torch.float32), rec).to(bf)
-                x = x + op(f"linear[{D}x{ff}]", lambda: lin["w2"][i].forward(m), rec).float()
-            return lin_out.forward(BK.rms_norm(x[-1:], lw["norm"], 1e-5, bf))
-        l_pre = timed(l_prefill, 3, 2)
-        l_prefill(True); lk.clear(); l_prefill(True)
-        del lm, eng, lw, lin, lin_out
-        torch.cuda.empty_cache()
-
+        l_pre, l_dec, lk = llama_beside(pkg, S, BK, z, hd, P, B, CTX, K, W, blocks_per, toks, timed, dev)
         med = lambda v: sorted(v)[len(v) // 2]
         esz = 2
         Gd = H // 2                                    # key heads of the recurrent layers
@@ -846,10 +857,212 @@ def run_gobesun(args):
                       "gpu_launches": int(pkg.lib().b200_total_kernel_launches() - l0), "sizes": results}))
 
 
+# ------------------------------------------------------------------------------------------------
+# --arch guvusun: latent attention + routed experts beside the closest existing model and kernels at equal size
+# ------------------------------------------------------------------------------------------------
+GUVUSUN_SIZES = {
+    # width, heads, unrotated / rotated / value sizes, latent, experts x ff (top + identity, groups), layers
+    "w2048": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, experts=64, ff=1408, top=6, identity=4, groups=(4, 2), vocab=32000, layers=4, side=64),
+    "w4096": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, rank=512, experts=32, ff=2048, top=4, identity=0, groups=None, vocab=32000, layers=2, side=64),
+}
+
+
+def run_guvusun(args):
+    import torch
+    import candle_vllm_b200 as pkg
+    from candle_vllm_b200 import seq_ops as ops, synthetic as S, mla as MLA
+    from candle_vllm_b200 import backend as BK
+    from candle_vllm_b200.engine import ModelRunner
+    from candle_vllm_b200.guvusun import GuvusunConfig, GuvusunModel
+
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else \
+        {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+    HBM, TC = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    props = torch.cuda.get_device_properties(0)
+    F32 = props.multi_processor_count * 128 * 2 * 1.965e9           # nominal f32 FMA rate: the bound of 32-bit SIMT arithmetic
+    K, W = max(args.steps, 1), max(args.warmup, 3)
+    P, B, CTX = 4096, 32, 1024
+    bf = torch.bfloat16
+    l0 = pkg.lib().b200_total_kernel_launches()
+
+    def timed(fn, reps, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e-3
+
+    sampler = ClockSampler(0); sampler.start()
+    results = {}
+    sizes = args.arch_sizes if args.arch_sizes != "w2048,w4096" else "w2048,w4096"
+    for name in [n for n in sizes.split(",") if n in GUVUSUN_SIZES]:
+        z = GUVUSUN_SIZES[name]
+        D, H, dn, dr, dv, R, E, ff, top, NL, V = z["width"], z["heads"], z["dim"], z["rot"], z["vdim"], z["rank"], z["experts"], z["ff"], z["top"], z["layers"], z["vocab"]
+        layers = [S.guvusun_layer(H, dn, dr, dv, R, experts=E, ff=ff, top=top, identity=z["identity"], groups=z["groups"], router_scale=1.8, base=1e6,
+                                  kv_from=(0 if i == NL - 1 and NL > 1 else None)) for i in range(NL)]
+        cfg = S.guvusun_config(D, V, layers, bigram=dict(buckets=65521, mul_prev=8191, mul_cur=131), side_dim=z["side"])
+        model = GuvusunModel(GuvusunConfig.from_dict(cfg), S.guvusun_weights(cfg, 0), dtype=bf, block_size=64, max_pos=P + 64, device=dev)
+        blocks_per = -(-(CTX + K + W + 8) // 64)
+        runner = ModelRunner(model, B * blocks_per + P // 64 + 1, B + 1, 64, decode_graphs=True, max_blocks_per_seq=blocks_per)
+        toks = torch.randint(0, V, (P,), generator=torch.Generator().manual_seed(1)).tolist()
+
+        def g_prefill():
+            runner.admit(10 ** 6)
+            runner.execute([dict(seq_id=10 ** 6, tokens=toks, want=[P - 1])])
+            runner.release(10 ** 6)
+        g_pre = timed(g_prefill, 3, 2)
+        for i in range(B):
+            runner.admit(i)
+        for i in range(0, B, 4):
+            runner.execute([dict(seq_id=j, tokens=toks[:CTX], want=[]) for j in range(i, i + 4)])
+        step_entries = lambda: [dict(seq_id=j, tokens=[toks[j]], want=[0]) for j in range(B)]
+        g_dec = timed(lambda: runner.execute(step_entries()), K, W)
+        g_dec_dev = timed(runner._graphs[B].graph.replay, K, 3)
+        # ---- per-kernel times from the model's own call sequence (eager, CUDA events around every op) ----------------------------
+        kern = {}
+        names = ["linear", "linear_grouped", "rms_norm_ex", "residual_rms_norm", "embedding_bigram", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb",
+                 "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down_combine", "moe_sorted_rows", "moe_gather_rows", "silu_mul_packed",
+                 "moe_combine_rows"]
+        orig = {n: getattr(ops, n) for n in names}
+
+        def instrument(tag):
+            def wrap(n):
+                def f(*a, **k):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize(); e0.record()
+                    r = orig[n](*a, **k)
+                    e1.record(); torch.cuda.synchronize()
+                    key = n
+                    if n == "linear":
+                        key = f"linear[{a[1].shape[0]}x{a[1].shape[1]}]"
+                    elif n == "linear_grouped":
+                        key = f"linear_grouped[{a[1].shape[0]}x{a[1].shape[1]}x{a[1].shape[2]}]"
+                    kern.setdefault((tag, key), []).append(e0.elapsed_time(e1) * 1e-3)
+                    return r
+                return f
+            for n in names:
+                setattr(ops, n, wrap(n))
+        instrument("prefill")
+        g_prefill(); kern.clear(); g_prefill()
+        runner.decode_graphs = False
+        instrument("decode")
+        runner.execute(step_entries())
+        for k in [k for k in kern if k[0] == "decode"]:
+            kern.pop(k)
+        runner.execute(step_entries())
+        for n in names:
+            setattr(ops, n, orig[n])
+        del runner, model
+        torch.cuda.empty_cache()
+
+        # ---- the closest existing kernels: latent attention of the DeepSeek path (absorbed form, R = 512, rotated part 64, bf16) -----
+        like = {}
+        if R == 512 and dr == 64:
+            g = torch.Generator().manual_seed(3)
+            nb = P // 64 + B * blocks_per
+            ckv = (torch.randn(nb, 64, 1, R, generator=g) * 0.5).to(bf).to(dev)
+            kpe = (torch.randn(nb, 64, 1, dr, generator=g) * 0.5).to(bf).to(dev)
+            qa = (torch.randn(P, H, R, generator=g) * 0.1).to(bf).to(dev)
+            qp = (torch.randn(P, H, dr, generator=g) * 0.1).to(bf).to(dev)
+            bt = torch.arange(P // 64, dtype=torch.int32, device=dev)[None, :]
+            ctx1 = torch.tensor([P], dtype=torch.int32, device=dev)
+            cu = torch.tensor([0, P], dtype=torch.int32, device=dev)
+            like["mla_paged_prefill"] = timed(lambda: MLA.mla_paged_prefill(qa, qp, ckv, kpe, bt, ctx1, cu, 0.07), 2, 1)
+            btd = torch.from_numpy(np.asarray(S.random_block_tables(B, blocks_per, nb, seed=2), np.int32)).to(dev)
+            ctxd = torch.full((B,), CTX + 1, dtype=torch.int32, device=dev)
+            like["mla_paged_decode"] = timed(lambda: MLA.mla_paged_decode(qa[:B].contiguous(), qp[:B].contiguous(), ckv, kpe, btd, ctxd, 0.07), 20, 3)
+            del ckv, kpe, qa, qp
+        # ---- dense bf16 Llama of equal width / heads / depth, ff = the experts a token uses -----------------------------------------
+        zl = dict(width=D, heads=H, kv=H // 4, ff=(top * ff + 127) // 128 * 128, vocab=V, layers=NL)
+        l_pre, l_dec, lk = llama_beside(pkg, S, BK, zl, 128, P, B, CTX, K, W, blocks_per, toks, timed, dev)
+        torch.cuda.empty_cache()
+
+        med = lambda v: sorted(v)[len(v) // 2]
+        esz = 2
+        Wd = R + dr
+
+        def work(tag, key, T):
+            """algorithmic work per call: ("bytes", n) against the measured copy bandwidth, ("flops", n) against the measured bf16 GEMM rate,
+            ("f32", n) against the nominal f32 FMA rate"""
+            if key.startswith("linear["):
+                n, k = (int(v) for v in key[7:-1].split("x"))
+                if n == V and tag == "prefill":
+                    T = 1
+                return ("flops", 2.0 * T * n * k) if (tag == "prefill" and T > 1) else ("bytes", n * k * esz + T * (k * esz + n * 4))
+            if key.startswith("linear_grouped["):
+                gcount, n, k = (int(v) for v in key[15:-1].split("x"))
+                rows = T * top if gcount == E else T * H
+                return ("flops", 2.0 * rows * n * k)
+            ctx_sum = T * (T + 1) / 2 if tag == "prefill" else T * (CTX + 1)
+            return {
+                "rms_norm_ex": ("bytes", (1 if tag == "prefill" else T) * D * (4 + esz)), "rms_norm": ("bytes", T * D * (4 + esz)),
+                "residual_rms_norm": ("bytes", T * D * (12 + esz)),
+                "embedding_bigram": ("bytes", T * D * (2 * esz + 4)),
+                "gelu_tanh_gather_mul": ("bytes", T * z["side"] * (4 + 2 * esz)),
+                "latent_kv_rope_cache": ("bytes", T * Wd * (4 + esz)),
+                "latent_q_absorb": ("bytes", T * H * ((dn + dr) * 4 + Wd * 4 + (dn * esz if tag == "prefill" else 0)) + (0 if tag == "prefill" else H * dn * R * esz)),
+                "latent_out_gate": ("bytes", T * H * ((dv if tag == "prefill" else R) * 4 + dv * esz) + (0 if tag == "prefill" else H * dv * R * esz)),
+                # scores and weighted sums over the latent: 2 (R + dr) + 2 R flops per key and head; in decode the cache rows of every
+                # sequence are read once per group of 8 heads
+                "latent_attention_varlen": ("f32", ctx_sum * H * (2 * Wd + 2 * R)) if tag == "prefill" else ("bytes", ctx_sum * Wd * esz),
+                "mla_paged_prefill": ("f32", ctx_sum * H * (2 * Wd + 2 * R)), "mla_paged_decode": ("bytes", ctx_sum * Wd * esz),
+                "moe_route": ("bytes", T * ((E + z["identity"]) * 4 + top * 8)),
+                "moe_gate_up": ("bytes", min(T * top, E) * 2 * ff * D * esz), "moe_down_combine": ("bytes", min(T * top, E) * ff * D * esz),
+                "moe_gather_rows": ("bytes", T * top * D * esz * 2), "silu_mul_packed": ("bytes", T * top * ff * (8 + esz)),
+                "moe_combine_rows": ("bytes", T * top * D * 4 + T * D * 8), "moe_sorted_rows": ("bytes", T * top * 12),
+                "silu_mul": ("bytes", T * zl["ff"] * (8 + esz)), "fused_rope": ("bytes", T * (H + zl["kv"]) * 128 * 8),
+                "reshape_and_cache": ("bytes", T * 2 * zl["kv"] * 128 * esz * 2), "paged_attention_prefill": ("flops", 4.0 * H * 128 * T * (T + 1) / 2),
+            }.get(key)
+
+        def table(rows, tag, T):
+            out = {}
+            for key, v in rows:
+                w = work(tag, key, T)
+                t = med(v)
+                e = {"us": round(t * 1e6, 1), "calls_per_step": len(v)}
+                if w:
+                    roof = w[1] / {"bytes": HBM, "flops": TC, "f32": F32}[w[0]]
+                    e.update(bound=w[0], roofline_us=round(roof * 1e6, 2), frac_of_peak=round(roof / t, 3))
+                out[key] = e
+            return out
+        results[name] = {
+            "guvusun": {"prefill_tokens_per_s": round(P / g_pre), "prefill_ms": round(g_pre * 1e3, 2), "decode_tokens_per_s": round(B / g_dec),
+                        "decode_ms_per_step": round(g_dec * 1e3, 3), "decode": "CUDA-graph replay incl. host metadata and H2D",
+                        "decode_ms_per_step_device": round(g_dec_dev * 1e3, 3), "decode_tokens_per_s_device": round(B / g_dec_dev),
+                        "kernels_prefill": table([(k[1], v) for k, v in kern.items() if k[0] == "prefill"], "prefill", P),
+                        "kernels_decode": table([(k[1], v) for k, v in kern.items() if k[0] == "decode"], "decode", B)},
+            "like_kernels": {"prefill": table([("mla_paged_prefill", [like["mla_paged_prefill"]])] if like else [], "prefill", P),
+                             "decode": table([("mla_paged_decode", [like["mla_paged_decode"]])] if like else [], "decode", B)},
+            "llama_dense_bf16": {"prefill_tokens_per_s": round(P / l_pre), "prefill_ms": round(l_pre * 1e3, 2), "decode_tokens_per_s": round(B / l_dec),
+                                 "decode_ms_per_step": round(l_dec * 1e3, 3), "decode": "CUDA-graph replay, device-resident metadata",
+                                 "prefill": "layer written with the framework's operators (f32 glue through torch)", "ff": zl["ff"],
+                                 "kernels_prefill": table(list(lk.items()), "prefill", P)},
+            "shape": dict(z, prompt=P, decode_batch=B, decode_ctx=CTX),
+        }
+    clocks = sampler.stop()
+    first = results[next(iter(results))]
+    print(json.dumps({"metric": "Guvusun prefill / decode tokens/s beside dense bf16 Llama of equal size", "value": first["guvusun"]["decode_tokens_per_s"],
+                      "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "arch": "guvusun",
+                      "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "f32_fma_tflops_nominal": round(F32 / 1e12, 1),
+                                "source": "fallback" if peaks.get("fallback") else "MEASURED_PEAKS.json"},
+                      "l2": "weights and activations of a step exceed L2 (126 MB)", "clocks": clocks,
+                      "gpu_launches": int(pkg.lib().b200_total_kernel_launches() - l0), "sizes": results}))
+
+
 def main():
     args = parse()
     if args.arch == "gobesun":
         run_gobesun(args)
+        return
+    if args.arch == "guvusun":
+        run_guvusun(args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -77,14 +77,36 @@ moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __re
     for (int r = lane; r < top; r += 32) weights[(int64_t)t * top + r] = s[ids[(int64_t)t * top + r]] * norm;
 }
 
+// dot of a weight row with a vector held in shared memory as f32, lanes striding over the row; 16-byte loads when the row allows them
+template <typename T>
+__device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ v, int n, int lane) {
+    float a = 0.f;
+    constexpr int kVec = 16 / (int)sizeof(T);
+    if (n % kVec == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        for (int i = lane * kVec; i < n; i += 32 * kVec) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
+            const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int c = 0; c < kVec; ++c) a = fmaf(v[i + c], to_f32<T>(e[c]), a);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) a = fmaf(v[i], to_f32<T>(w[i]), a);
+    }
+    return a;
+}
+
+constexpr int kGuRows = 32;        // gate / up rows per block of moe_gate_up
+constexpr int kDownCols = 64;      // output columns per block of moe_down_combine
+
 template <typename T>
 __global__ void __launch_bounds__(128)
-moe_gate_up_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ w_gu, const int32_t* __restrict__ ids, T* __restrict__ act, int top, int E,
-                   int ff, int D) {
+moe_gate_up_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ w_gu, const int32_t* __restrict__ ids, const int32_t* __restrict__ order,
+                   T* __restrict__ act, int top, int E, int ff, int D) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float hs[];                          // [D]
-    const int64_t p = blockIdx.x;
+    const int64_t p = order ? (int64_t)order[blockIdx.x] : (int64_t)blockIdx.x;      // `order` walks the pairs expert by expert, so that blocks running together share weights
+    if (p < 0) return;
     const int e = ids[p];
     if (e < 0 || e >= E) return;                           // identity expert: nothing to compute
     const int64_t t = p / top;
@@ -92,11 +114,9 @@ moe_gate_up_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ w
     for (int i = threadIdx.x; i < D; i += 128) hs[i] = to_f32<T>(h[t * ldh + i]);
     __syncthreads();
     const T* wg = w_gu + (int64_t)e * 2 * ff * D;           // [gate rows | up rows][D]
-    for (int j = warp; j < ff; j += 4) {
-        const T* g = wg + (int64_t)j * D;
-        const T* u = wg + (int64_t)(ff + j) * D;
-        float a = 0.f, b = 0.f;
-        for (int i = lane; i < D; i += 32) { const float x = hs[i]; a = fmaf(x, to_f32<T>(g[i]), a); b = fmaf(x, to_f32<T>(u[i]), b); }
+    const int j1 = min(ff, (int)(blockIdx.y + 1) * kGuRows);
+    for (int j = blockIdx.y * kGuRows + warp; j < j1; j += 4) {
+        float a = row_dot<T>(wg + (int64_t)j * D, hs, D, lane), b = row_dot<T>(wg + (int64_t)(ff + j) * D, hs, D, lane);
         a = warp_sum(a); b = warp_sum(b);
         if (lane == 0) act[p * ff + j] = from_f32<T>(a / (1.0f + expf(-a)) * b);
     }
@@ -117,15 +137,14 @@ moe_down_combine_kernel(const T* __restrict__ act, const T* __restrict__ w_d, co
             for (int i = threadIdx.x; i < ff; i += 256) as[k * ff + i] = to_f32<T>(act[(t * top + k) * ff + i]);
     }
     __syncthreads();
-    for (int d = warp; d < D; d += 8) {
+    const int d1 = min(D, (int)(blockIdx.y + 1) * kDownCols);
+    for (int d = blockIdx.y * kDownCols + warp; d < d1; d += 8) {
         float tot = 0.f;
         for (int k = 0; k < top; ++k) {
             const int e = ids[t * top + k];
             const float wk = weights[t * top + k];
             if (e >= 0 && e < E) {
-                const T* w = w_d + ((int64_t)e * D + d) * ff;
-                float a = 0.f;
-                for (int i = lane; i < ff; i += 32) a = fmaf(as[k * ff + i], to_f32<T>(w[i]), a);
+                const float a = row_dot<T>(w_d + ((int64_t)e * D + d) * ff, as + k * ff, ff, lane);
                 tot = fmaf(wk, warp_sum(a), tot);
             } else {
                 tot = fmaf(wk, x[t * ldx + d], tot);
@@ -135,11 +154,9 @@ moe_down_combine_kernel(const T* __restrict__ act, const T* __restrict__ w_d, co
     }
 }
 
-constexpr int kTile = 128;
-
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ pair_row, int32_t* __restrict__ row_pair, int32_t* __restrict__ tile_group, int pairs,
-                 int E, int max_rows) {
+                 int E, int max_rows, int kTile) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ int sh[];
@@ -157,10 +174,12 @@ moe_align_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ pair_row
     }
     __syncthreads();
     for (int r = threadIdx.x; r < max_rows; r += 1024) row_pair[r] = -1;
-    for (int i = threadIdx.x; i < max_rows / kTile; i += 1024) tile_group[i] = -1;
+    if (tile_group)
+        for (int i = threadIdx.x; i < max_rows / kTile; i += 1024) tile_group[i] = -1;
     __syncthreads();
-    for (int e = threadIdx.x; e < E; e += 1024)
-        for (int i = start[e] / kTile; i < start[e + 1] / kTile; ++i) tile_group[i] = e;
+    if (tile_group)
+        for (int e = threadIdx.x; e < E; e += 1024)
+            for (int i = start[e] / kTile; i < start[e + 1] / kTile; ++i) tile_group[i] = e;
     for (int p = threadIdx.x; p < pairs; p += 1024) {
         const int e = ids[p];
         int row = -1;
@@ -229,19 +248,19 @@ void moe_route(const float* logits, int64_t ld, const float* correction, int32_t
     check_launch("moe_route");
 }
 
-void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, void* act, int32_t num_tokens, int32_t top, int32_t num_experts,
-                 int32_t ff, int32_t width, int32_t dtype, int64_t stream) {
+void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, const int32_t* order, void* act, int32_t num_tokens, int32_t top,
+                 int32_t num_experts, int32_t ff, int32_t width, int32_t dtype, int64_t stream) {
     if (num_tokens == 0 || num_experts == 0) return;
     B200_REQUIRE(h && w_gate_up && ids && act && top > 0 && ff > 0 && width > 0 && width <= 16384 && ldh >= width, kErrBadArg, "moe_gate_up: bad arguments");
     cudaStream_t st = as_stream(stream);
-    const dim3 grid((unsigned)((int64_t)num_tokens * top));
+    const dim3 grid((unsigned)((int64_t)num_tokens * top), (unsigned)((ff + kGuRows - 1) / kGuRows));
     const size_t smem = (size_t)width * sizeof(float);
     ensure_dynamic_smem(reinterpret_cast<const void*>(moe_gate_up_kernel<float>), (int)smem);
     ensure_dynamic_smem(reinterpret_cast<const void*>(moe_gate_up_kernel<__nv_bfloat16>), (int)smem);
     if (dtype == B200_F32)
-        launch_pdl(moe_gate_up_kernel<float>, grid, dim3(128), smem, st, (const float*)h, ldh, (const float*)w_gate_up, ids, (float*)act, top, num_experts, ff, width);
+        launch_pdl(moe_gate_up_kernel<float>, grid, dim3(128), smem, st, (const float*)h, ldh, (const float*)w_gate_up, ids, order, (float*)act, top, num_experts, ff, width);
     else if (dtype == B200_BF16)
-        launch_pdl(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(128), smem, st, (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w_gate_up, ids,
+        launch_pdl(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(128), smem, st, (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w_gate_up, ids, order,
                    (__nv_bfloat16*)act, top, num_experts, ff, width);
     else { set_error(kErrUnsupported, "moe_gate_up: dtype %d (f32 / bf16)", dtype); return; }
     count_launch();
@@ -258,28 +277,30 @@ void moe_down_combine(const void* act, const void* w_down, const int32_t* ids, c
     B200_REQUIRE(smem <= 160 * 1024, kErrUnsupported, "moe_down_combine: top * ff = %d floats do not fit shared memory", top * ff);
     if (dtype == B200_F32) {
         ensure_dynamic_smem(reinterpret_cast<const void*>(moe_down_combine_kernel<float>), (int)smem);
-        launch_pdl(moe_down_combine_kernel<float>, dim3(num_tokens), dim3(256), smem, st, (const float*)act, (const float*)w_down, ids, weights, x, ldx, out, top,
+        launch_pdl(moe_down_combine_kernel<float>, dim3(num_tokens, (width + kDownCols - 1) / kDownCols), dim3(256), smem, st, (const float*)act, (const float*)w_down, ids, weights, x, ldx, out, top,
                    num_experts, ff, width);
     } else if (dtype == B200_BF16) {
         ensure_dynamic_smem(reinterpret_cast<const void*>(moe_down_combine_kernel<__nv_bfloat16>), (int)smem);
-        launch_pdl(moe_down_combine_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(256), smem, st, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, ids,
+        launch_pdl(moe_down_combine_kernel<__nv_bfloat16>, dim3(num_tokens, (width + kDownCols - 1) / kDownCols), dim3(256), smem, st, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, ids,
                    weights, x, ldx, out, top, num_experts, ff, width);
     } else { set_error(kErrUnsupported, "moe_down_combine: dtype %d (f32 / bf16)", dtype); return; }
     count_launch();
     check_launch("moe_down_combine");
 }
 
-int64_t moe_align_rows(int64_t pairs, int32_t num_experts) {
-    // every expert's run is padded to whole tiles: at most kTile - 1 rows of padding each
-    return (pairs + (int64_t)num_experts * (kTile - 1) + kTile - 1) / kTile * kTile;
+int64_t moe_align_rows(int64_t pairs, int32_t num_experts, int32_t tile) {
+    // every expert's run is padded to whole tiles: at most tile - 1 rows of padding each
+    if (tile < 1) tile = 1;
+    return (pairs + (int64_t)num_experts * (tile - 1) + tile - 1) / tile * tile;
 }
 
-void moe_align(const int32_t* ids, int32_t* pair_row, int32_t* row_pair, int32_t* tile_group, int32_t pairs, int32_t num_experts, int32_t max_rows, int64_t stream) {
+void moe_align(const int32_t* ids, int32_t* pair_row, int32_t* row_pair, int32_t* tile_group, int32_t pairs, int32_t num_experts, int32_t max_rows, int32_t tile,
+               int64_t stream) {
     if (pairs == 0) return;
-    B200_REQUIRE(ids && pair_row && row_pair && tile_group && pairs > 0 && num_experts > 0 && num_experts <= 4096 && max_rows % kTile == 0 &&
-                 max_rows >= moe_align_rows(pairs, num_experts), kErrBadArg, "moe_align: bad arguments");
+    B200_REQUIRE(ids && pair_row && row_pair && (tile_group || tile == 1) && pairs > 0 && num_experts > 0 && num_experts <= 4096 && tile >= 1 &&
+                 max_rows % tile == 0 && max_rows >= moe_align_rows(pairs, num_experts, tile), kErrBadArg, "moe_align: bad arguments");
     launch_pdl(moe_align_kernel, dim3(1), dim3(1024), (size_t)(3 * num_experts + 1) * sizeof(int), as_stream(stream), ids, pair_row, row_pair, tile_group, pairs,
-               num_experts, max_rows);
+               num_experts, max_rows, tile);
     count_launch();
     check_launch("moe_align");
 }

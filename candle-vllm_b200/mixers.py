@@ -270,7 +270,11 @@ class RoutedExperts:
             act = ops.silu_mul_packed(gu, torch.bfloat16)
             y = ops.linear_grouped(act, self.w_d, tile_expert, torch.empty((xg.shape[0], self.w_d.shape[1]), dtype=torch.float32, device=h.device))
             return ops.moe_combine_rows(y, pair_row, wts, x)
-        act = ops.moe_gate_up(h, self.w_gu, ids) if self.E else None
+        act = None
+        if self.E:
+            # several tokens: the blocks walk the pairs expert by expert, so that those running together read the same weights
+            order = ops.moe_sorted_rows(ids, self.E, tile=1)[1] if h.shape[0] > 1 else None
+            act = ops.moe_gate_up(h, self.w_gu, ids, order)
         return ops.moe_down_combine(act, self.w_d, ids, wts, x, self.E, self.ff)
 
 

@@ -351,13 +351,14 @@ def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int
     return ids, w
 
 
-def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
-    """h [T, D], w_gate_up [E, 2 ff, D] of one dtype -> act [T * top, ff] (rows of identity choices are left unwritten)"""
+def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor, order: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h [T, D], w_gate_up [E, 2 ff, D] of one dtype -> act [T * top, ff] (rows of identity choices are left unwritten); ``order`` i32 [T * top]: the
+    pairs in the order the blocks take them (sorted by expert, so that neighbours share weights)"""
     T, D = h.shape
     E, ff2, _ = w_gate_up.shape
     top = ids.shape[1]
     act = torch.empty((T * top, ff2 // 2), dtype=h.dtype, device=h.device)
-    lib().moe_gate_up(_ptr(h), C.c_int64(h.stride(0) if T > 1 else max(D, h.stride(0))), _ptr(w_gate_up), _ptr(ids), _ptr(act), C.c_int32(T), C.c_int32(top), C.c_int32(E),
+    lib().moe_gate_up(_ptr(h), C.c_int64(h.stride(0) if T > 1 else max(D, h.stride(0))), _ptr(w_gate_up), _ptr(ids), _ptr(order), _ptr(act), C.c_int32(T), C.c_int32(top), C.c_int32(E),
                       C.c_int32(ff2 // 2), C.c_int32(D), C.c_int32(_tag(h.dtype)), _stream(h.device))
     check("moe_gate_up")
     return act
@@ -376,15 +377,16 @@ def moe_down_combine(act: Optional[torch.Tensor], w_down: Optional[torch.Tensor]
     return out
 
 
-def moe_sorted_rows(ids: torch.Tensor, num_experts: int):
-    """pairs (token, choice) sorted by expert into tiles of 128 rows -> (pair_row i32 [T * top] (-1 for identity choices), row_pair i32 [rows] (-1 =
-    padding), tile_group i32 [rows / 128] (-1 = unused tile)); rows = an upper bound that depends on the counts only through their number"""
+def moe_sorted_rows(ids: torch.Tensor, num_experts: int, tile: int = 128):
+    """pairs (token, choice) sorted by expert into tiles of ``tile`` rows -> (pair_row i32 [T * top] (-1 for identity choices), row_pair i32 [rows] (-1
+    = padding), tile_group i32 [rows / tile] (-1 = unused tile)); rows = an upper bound that depends on the counts only through their number"""
     P = ids.numel()
-    rows = int(lib().moe_align_rows(C.c_int64(P), C.c_int32(num_experts)))
+    rows = int(lib().moe_align_rows(C.c_int64(P), C.c_int32(num_experts), C.c_int32(tile)))
     pair_row = torch.empty((P,), dtype=torch.int32, device=ids.device)
     row_pair = torch.empty((rows,), dtype=torch.int32, device=ids.device)
-    tile_group = torch.empty((rows // 128,), dtype=torch.int32, device=ids.device)
-    lib().moe_align(_ptr(ids), _ptr(pair_row), _ptr(row_pair), _ptr(tile_group), C.c_int32(P), C.c_int32(num_experts), C.c_int32(rows), _stream(ids.device))
+    tile_group = torch.empty((rows // tile,), dtype=torch.int32, device=ids.device)
+    lib().moe_align(_ptr(ids), _ptr(pair_row), _ptr(row_pair), _ptr(tile_group), C.c_int32(P), C.c_int32(num_experts), C.c_int32(rows), C.c_int32(tile),
+                    _stream(ids.device))
     check("moe_align")
     return pair_row, row_pair, tile_group
 

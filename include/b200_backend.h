@@ -495,7 +495,8 @@ void b200_allreduce_f32(void* nccl_comm, float* buf, int64_t n, int64_t stream);
  * moe_route: logits f32 [T, N] -> ids i32 [T, top], weights f32 [T, top]: softmax over N; choice = softmax + correction (f32 [N] or null); only
  *   members of the `keep` groups (of `groups` equal runs of neighbours) with the best single choice score may be taken; weights = softmax of the
  *   taken / (their sum + 1e-20) * scale.  groups <= 1: no restriction.
- * moe_gate_up: act [T top, ff] = silu(W_gate[e] h_t) * (W_up[e] h_t) for every pair with e = ids[p] < num_experts; w_gate_up [E, 2 ff, width].
+ * moe_gate_up: act [T top, ff] = silu(W_gate[e] h_t) * (W_up[e] h_t) for every pair with e = ids[p] < num_experts; w_gate_up [E, 2 ff, width]; order
+ *   (i32 [T top] or null) = the pairs in the order the blocks take them (negative = none), e.g. row_pair of moe_align with tile 1.
  * moe_down_combine: out f32 [T, width] = sum_k weights[t, k] * (W_down[e] act[t, k]) (e < num_experts) or weights[t, k] * x[t] (identity expert);
  *   w_down [E, width, ff]. */
 void embedding_bigram(const void* table, const void* bigram, const int32_t* ids, const int32_t* positions, const int32_t* token_seq,
@@ -520,24 +521,25 @@ void latent_out_gate(const float* src, int64_t src_stride_token, int64_t src_str
 /* linear_grouped: out[r, :n] (out_dtype F32 / BF16, row pitch ldy) = x[r, :k] . weight[tile_group[r / 128]]^T: bf16 x [m_pad, k] (row pitch ldx, m_pad a
  *   multiple of 128) whose rows come in tiles of 128 that each multiply one matrix of the bf16 stack weight [groups, n, k]; tile_group i32 [m_pad / 128] on
  *   the device, a negative entry skips the tile.  The tcgen05 GEMM of linear_16bit with the weight tile chosen per row tile.
- * moe_align: pairs (token, choice) sorted by expert into tiles of 128 rows: ids i32 [pairs]; pair_row[p] = its row in the sorted, padded order (-1 for an
- *   identity choice, id >= num_experts), row_pair i32 [max_rows] the inverse (-1 = padding), tile_group i32 [max_rows / 128] the expert of every tile (-1 =
- *   unused); max_rows >= moe_align_rows(pairs, num_experts).
+ * moe_align: pairs (token, choice) sorted by expert into tiles of `tile` rows (128 for linear_grouped; 1 = plain sort): ids i32 [pairs]; pair_row[p] = its
+ *   row in the sorted, padded order (-1 for an identity choice, id >= num_experts), row_pair i32 [max_rows] the inverse (-1 = padding), tile_group i32
+ *   [max_rows / tile] the expert of every tile (-1 = unused; may be null when tile == 1); max_rows >= moe_align_rows(pairs, num_experts, tile).
  * moe_gather_rows: xg bf16 [max_rows, width] = h[row_pair[r] / top] (zeros for padding).
  * silu_mul_packed: out[r, :ff] = silu(gu[r, :ff]) * gu[r, ff : 2 ff] from f32 gu, out_dtype F32 / BF16.
  * moe_combine_rows: out f32 [T, width] = sum_k weights[t, k] * (pair_row >= 0 ? y[pair_row[t, k]] : x[t]), in choice order. */
 void linear_grouped(const void* x, const void* weight, void* out, const int32_t* tile_group, int32_t m_pad, int32_t n, int32_t k, int32_t groups, int64_t ldx,
                     int64_t ldy, int32_t out_dtype, int64_t stream);
-int64_t moe_align_rows(int64_t pairs, int32_t num_experts);
-void moe_align(const int32_t* ids, int32_t* pair_row, int32_t* row_pair, int32_t* tile_group, int32_t pairs, int32_t num_experts, int32_t max_rows, int64_t stream);
+int64_t moe_align_rows(int64_t pairs, int32_t num_experts, int32_t tile);
+void moe_align(const int32_t* ids, int32_t* pair_row, int32_t* row_pair, int32_t* tile_group, int32_t pairs, int32_t num_experts, int32_t max_rows, int32_t tile,
+               int64_t stream);
 void moe_gather_rows(const void* h, int64_t ldh, const int32_t* row_pair, void* xg, int32_t max_rows, int32_t top, int32_t width, int64_t stream);
 void silu_mul_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, int64_t ld, int32_t out_dtype, int64_t stream);
 void moe_combine_rows(const float* y, const int32_t* pair_row, const float* weights, const float* x, int64_t ldx, float* out, int32_t num_tokens, int32_t top,
                       int32_t width, int64_t stream);
 void moe_route(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* weights, int32_t num_tokens, int32_t num_outputs, int32_t top,
                int32_t groups, int32_t keep, float scale, int64_t stream);
-void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, void* act, int32_t num_tokens, int32_t top, int32_t num_experts,
-                 int32_t ff, int32_t width, int32_t dtype, int64_t stream);
+void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, const int32_t* order, void* act, int32_t num_tokens, int32_t top,
+                 int32_t num_experts, int32_t ff, int32_t width, int32_t dtype, int64_t stream);
 void moe_down_combine(const void* act, const void* w_down, const int32_t* ids, const float* weights, const float* x, int64_t ldx, float* out,
                       int32_t num_tokens, int32_t top, int32_t num_experts, int32_t ff, int32_t width, int32_t dtype, int64_t stream);
 
