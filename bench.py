@@ -928,7 +928,7 @@ def run_guvusun(args):
         # ---- per-kernel times from the model's own call sequence (eager, CUDA events around every op) ----------------------------
         kern = {}
         names = ["linear", "linear_grouped", "rms_norm_ex", "residual_rms_norm", "embedding_bigram", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb",
-                 "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down_combine", "moe_sorted_rows", "moe_gather_rows", "silu_mul_packed",
+                 "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "moe_sorted_rows", "moe_gather_rows", "silu_mul_packed",
                  "moe_combine_rows"]
         orig = {n: getattr(ops, n) for n in names}
 
@@ -1014,7 +1014,7 @@ def run_guvusun(args):
                 "latent_attention_varlen": ("f32", ctx_sum * H * (2 * Wd + 2 * R)) if tag == "prefill" else ("bytes", ctx_sum * Wd * esz),
                 "mla_paged_prefill": ("f32", ctx_sum * H * (2 * Wd + 2 * R)), "mla_paged_decode": ("bytes", ctx_sum * Wd * esz),
                 "moe_route": ("bytes", T * ((E + z["identity"]) * 4 + top * 8)),
-                "moe_gate_up": ("bytes", min(T * top, E) * 2 * ff * D * esz), "moe_down_combine": ("bytes", min(T * top, E) * ff * D * esz),
+                "moe_gate_up": ("bytes", min(T * top, E) * 2 * ff * D * esz), "moe_down": ("bytes", min(T * top, E) * ff * D * esz),
                 "moe_gather_rows": ("bytes", T * top * D * esz * 2), "silu_mul_packed": ("bytes", T * top * ff * (8 + esz)),
                 "moe_combine_rows": ("bytes", T * top * D * 4 + T * D * 8), "moe_sorted_rows": ("bytes", T * top * 12),
                 "silu_mul": ("bytes", T * zl["ff"] * (8 + esz)), "fused_rope": ("bytes", T * (H + zl["kv"]) * 128 * 8),

@@ -15,7 +15,8 @@
 //                            W_uk product on the tensor-core GEMM instead and call this with w_uk = null for the rotation alone).
 //   latent_attention_varlen  one block per (token, group of heads): tiles of 32 keys are staged once in shared memory for all heads of
 //                            the group, a lane scores one key, then the tile's latents are accumulated with lanes across the
-//                            latent columns; online softmax in f32 that starts from the sink.
+//                            latent columns; online softmax in f32 that starts from the sink.  Steps of few rows cut every row's keys into
+//                            `splits` runs (one block each) whose (max, sum, weighted sum) a second kernel folds.
 //   latent_out_gate          out as above (w_uv = null: the product was done by the GEMM, only the gate and the cast remain).
 #include "common.cuh"
 
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(256)
 latent_attention_varlen_kernel(const float* __restrict__ q_lat, int64_t q_st, int64_t q_sh, const TC* __restrict__ c_cache, const TC* __restrict__ kr_cache,
                                const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ token_seq,
                                const int32_t* __restrict__ positions, const float* __restrict__ sink, TO* __restrict__ o_lat, int64_t o_st, int64_t o_sh,
-                               int H, int R, int dr, int block_size, float scale, int window, int groups_per_token) {
+                               int H, int R, int dr, int block_size, float scale, int window, int groups_per_token, int splits, float* __restrict__ part) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float sm[];
@@ -107,7 +108,7 @@ latent_attention_varlen_kernel(const float* __restrict__ q_lat, int64_t q_st, in
     const int t = blockIdx.x / groups_per_token;
     const int h = (blockIdx.x - t * groups_per_token) * nw + warp;
     const bool live = h < H;
-    const int pos = positions[t];
+    int pos = positions[t];
     const int32_t* table = block_tables + (int64_t)token_seq[t] * table_width;
     if (live) {
         const float* q = q_lat + (int64_t)t * q_st + (int64_t)h * q_sh;
@@ -115,11 +116,21 @@ latent_attention_varlen_kernel(const float* __restrict__ q_lat, int64_t q_st, in
     }
     int lo = 0;
     if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
-    // the sink is a key without a value whose score is sink[h] as it stands
-    float m = (live && sink) ? sink[h] : -INFINITY, l = (live && sink) ? 1.f : 0.f;
+    int hi = pos;
+    const int split = blockIdx.y;
+    if (splits > 1) {
+        // the row's keys are cut into `splits` runs of whole 32-key tiles; this block takes run blockIdx.y and leaves (m, l, sum) for the merge
+        const int run = (((pos - lo + 1) + splits - 1) / splits + 31) / 32 * 32;
+        lo += split * run;
+        hi = min(pos, lo + run - 1);
+    }
+    // the sink is a key without a value whose score is sink[h] as it stands (it joins the first run only)
+    const bool with_sink = live && sink && split == 0;
+    float m = with_sink ? sink[h] : -INFINITY, l = with_sink ? 1.f : 0.f;
     float acc[NR];
 #pragma unroll
     for (int c = 0; c < NR; ++c) acc[c] = 0.f;
+    pos = hi;
     for (int j0 = lo; j0 <= pos; j0 += 32) {
         __syncthreads();                                   // q staged / previous tile consumed
         for (int kk = warp; kk < 32; kk += nw) {
@@ -150,7 +161,7 @@ latent_attention_varlen_kernel(const float* __restrict__ q_lat, int64_t q_st, in
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
-        const float corr = expf(m - m_new);                // m = -inf only before the first tile of a sink-less head: l and acc are 0
+        const float corr = m == -INFINITY ? 0.f : expf(m - m_new);      // m = -inf only before the first tile of a sink-less run: l and acc are 0
         l = l * corr + warp_sum(p);
         m = m_new;
 #pragma unroll
@@ -167,11 +178,47 @@ latent_attention_varlen_kernel(const float* __restrict__ q_lat, int64_t q_st, in
         }
     }
     if (!live) return;
+    if (splits > 1) {
+        float* dst = part + (((int64_t)t * H + h) * splits + split) * (R + 2);
+        if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+        for (int c = 0; c < NR; ++c) {
+            const int i = lane + 32 * c;
+            if (i < R) dst[2 + i] = acc[c];
+        }
+        return;
+    }
     const float inv = 1.0f / l;
 #pragma unroll
     for (int c = 0; c < NR; ++c) {
         const int i = lane + 32 * c;
         if (i < R) o_lat[(int64_t)t * o_st + (int64_t)h * o_sh + i] = from_f32<TO>(acc[c] * inv);
+    }
+}
+
+// folds the runs of a split row: with M = max m_s, out = sum_s exp(m_s - M) sum_s / sum_s exp(m_s - M) l_s (a run without keys has m = -inf, l = 0)
+template <typename TO>
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ part, TO* __restrict__ o_lat, int64_t o_st, int64_t o_sh, int H, int R, int splits) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float* src = part + ((int64_t)t * H + h) * splits * (R + 2);
+    float M = -INFINITY;
+    for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, src[(int64_t)s2 * (R + 2)]);
+    float L = 0.f;
+    for (int s2 = 0; s2 < splits; ++s2) {
+        const float ms = src[(int64_t)s2 * (R + 2)];
+        if (ms != -INFINITY) L = fmaf(expf(ms - M), src[(int64_t)s2 * (R + 2) + 1], L);
+    }
+    const float inv = 1.0f / L;
+    for (int i = threadIdx.x; i < R; i += 128) {
+        float a = 0.f;
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float ms = src[(int64_t)s2 * (R + 2)];
+            if (ms != -INFINITY) a = fmaf(expf(ms - M), src[(int64_t)s2 * (R + 2) + 2 + i], a);
+        }
+        o_lat[(int64_t)t * o_st + (int64_t)h * o_sh + i] = from_f32<TO>(a * inv);
     }
 }
 
@@ -253,9 +300,12 @@ void latent_q_absorb(const float* proj, int64_t ld, const void* w_uk, const floa
 void latent_attention_varlen(void* o_lat, int64_t o_stride_token, int64_t o_stride_head, int32_t out_dtype, const float* q_lat, int64_t q_stride_token,
                              int64_t q_stride_head, const void* c_cache, const void* kr_cache, const int32_t* block_tables, int32_t table_width,
                              const int32_t* token_seq, const int32_t* positions, const float* sink, int32_t num_tokens, int32_t num_heads, int32_t rank,
-                             int32_t rot_dim, int32_t block_size, float scale, int32_t window, int32_t cache_dtype, int64_t stream) {
+                             int32_t rot_dim, int32_t block_size, float scale, int32_t window, int32_t cache_dtype, int32_t splits, float* partials,
+                             int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(o_lat && q_lat && c_cache && kr_cache && block_tables && token_seq && positions, kErrBadArg, "latent_attention_varlen: null pointer");
+    B200_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || partials) && num_heads <= 65535, kErrBadArg, "latent_attention_varlen: %d runs need a partials buffer",
+                 splits);
     B200_REQUIRE(num_heads > 0 && rank > 0 && rot_dim >= 0 && block_size > 0 && table_width > 0 && window >= 0, kErrBadArg, "latent_attention_varlen: bad sizes");
     B200_REQUIRE(rank <= 1024, kErrUnsupported, "latent_attention_varlen: latent size %d > 1024", rank);
     cudaStream_t st = as_stream(stream);
@@ -264,13 +314,14 @@ void latent_attention_varlen(void* o_lat, int64_t o_stride_token, int64_t o_stri
     const int W = rank + rot_dim;
     const size_t smem = ((size_t)nw * W + (size_t)32 * (W | 1)) * sizeof(float);
     B200_REQUIRE(smem <= 200 * 1024, kErrUnsupported, "latent_attention_varlen: latent + rotated size %d does not fit shared memory", W);
-    const dim3 grid((unsigned)((int64_t)num_tokens * groups));
+    const dim3 grid((unsigned)((int64_t)num_tokens * groups), (unsigned)splits);
 #define LAV(TC, TO, NR)                                                                                                                             \
     do {                                                                                                                                            \
         auto kern = latent_attention_varlen_kernel<TC, TO, NR>;                                                                                     \
         ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem);                                                                        \
         launch_pdl(kern, grid, dim3(nw * 32), smem, st, q_lat, q_stride_token, q_stride_head, (const TC*)c_cache, (const TC*)kr_cache, block_tables, table_width,  \
-                   token_seq, positions, sink, (TO*)o_lat, o_stride_token, o_stride_head, num_heads, rank, rot_dim, block_size, scale, window, groups);  \
+                   token_seq, positions, sink, (TO*)o_lat, o_stride_token, o_stride_head, num_heads, rank, rot_dim, block_size, scale, window, groups, splits, \
+                   partials);                                                                                                                       \
     } while (0)
 #define LAV_R(TC, TO)                                                                                                                               \
     do {                                                                                                                                            \
@@ -283,6 +334,15 @@ void latent_attention_varlen(void* o_lat, int64_t o_stride_token, int64_t o_stri
 #undef LAV_R
 #undef LAV
     count_launch();
+    if (splits > 1) {
+        const dim3 mg(num_tokens, num_heads);
+        if (out_dtype == B200_F32)
+            launch_pdl(latent_attention_merge_kernel<float>, mg, dim3(128), 0, st, (const float*)partials, (float*)o_lat, o_stride_token, o_stride_head, num_heads, rank, splits);
+        else
+            launch_pdl(latent_attention_merge_kernel<__nv_bfloat16>, mg, dim3(128), 0, st, (const float*)partials, (__nv_bfloat16*)o_lat, o_stride_token, o_stride_head,
+                       num_heads, rank, splits);
+        count_launch();
+    }
     check_launch("latent_attention_varlen");
 }
 

@@ -8,11 +8,12 @@
 //                     index); weights = s of the chosen / (their sum + 1e-20) * scale.  groups <= 1 switches the restriction off.
 //   moe_gate_up       act[p] = silu(W_gate[e] h) * (W_up[e] h) for pair p = (token, choice) with expert e < E; outputs e >= E are identity
 //                     experts (no weights) and are skipped.
-//   moe_down_combine  out[t] = sum over the token's choices, in choice order, of weight * (W_down[e] act[p]), or weight * x[t] for an
+//   moe_down          y[row] = W_down[e] act[p] for the pairs in expert order (moe_align with tiles of one row);
+//   moe_combine_rows  out[t] = sum over the token's choices, in choice order, of weight * y[row of the pair], or weight * x[t] for an
 //                     identity expert.
 // Steps with many rows (bf16): moe_align sorts the pairs by expert into tiles of 128 rows (padding each expert's run), moe_gather_rows copies
 // the tokens' rows into that order, the two expert products run as grouped tcgen05 GEMMs (dense_gemm.cu, the weight tile chosen per row tile),
-// silu_mul_packed sits between them, and moe_combine_rows adds each token's choices in choice order -- the same sum as moe_down_combine.
+// silu_mul_packed sits between them, and the same moe_combine_rows adds each token's choices in choice order.
 #include "common.cuh"
 
 namespace b200 {
@@ -77,17 +78,30 @@ moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __re
     for (int r = lane; r < top; r += 32) weights[(int64_t)t * top + r] = s[ids[(int64_t)t * top + r]] * norm;
 }
 
-// dot of a weight row with a vector held in shared memory as f32, lanes striding over the row; 16-byte loads when the row allows them
+// Dot of a weight row with a vector staged in shared memory as f32, lanes striding over the row.  When rows allow 16-byte loads (`vec`) a lane
+// takes kVec consecutive weights at once and the vector is staged so that element i sits at (i % kVec) * (n / kVec) + i / kVec: for each of
+// the kVec sub-steps the lanes then read consecutive words (no bank conflicts).
 template <typename T>
-__device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ v, int n, int lane) {
+__device__ __forceinline__ bool rows_vectorise(const T* base, int n, int64_t pitch) {
+    constexpr int kVec = 16 / (int)sizeof(T);
+    return n % kVec == 0 && pitch % kVec == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+}
+template <typename T>
+__device__ __forceinline__ int staged_at(int i, int n, bool vec) {
+    constexpr int kVec = 16 / (int)sizeof(T);
+    return vec ? (i % kVec) * (n / kVec) + i / kVec : i;
+}
+template <typename T>
+__device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ v, int n, int lane, bool vec) {
     float a = 0.f;
     constexpr int kVec = 16 / (int)sizeof(T);
-    if (n % kVec == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
-        for (int i = lane * kVec; i < n; i += 32 * kVec) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
+    if (vec) {
+        const int nv = n / kVec;
+        for (int i = lane; i < nv; i += 32) {
+            const uint4 raw = reinterpret_cast<const uint4*>(w)[i];
             const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-            for (int c = 0; c < kVec; ++c) a = fmaf(v[i + c], to_f32<T>(e[c]), a);
+            for (int c = 0; c < kVec; ++c) a = fmaf(v[c * nv + i], to_f32<T>(e[c]), a);
         }
     } else {
         for (int i = lane; i < n; i += 32) a = fmaf(v[i], to_f32<T>(w[i]), a);
@@ -96,7 +110,7 @@ __device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* _
 }
 
 constexpr int kGuRows = 32;        // gate / up rows per block of moe_gate_up
-constexpr int kDownCols = 64;      // output columns per block of moe_down_combine
+constexpr int kDownCols = 64;      // output columns per block of moe_down
 
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -105,52 +119,45 @@ moe_gate_up_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ w
     pdl_wait();
     pdl_trigger();
     extern __shared__ float hs[];                          // [D]
-    const int64_t p = order ? (int64_t)order[blockIdx.x] : (int64_t)blockIdx.x;      // `order` walks the pairs expert by expert, so that blocks running together share weights
+    const int64_t p = order ? (int64_t)order[blockIdx.x] : (int64_t)blockIdx.x;      // `order` walks the pairs expert by expert: blocks running together share weights
     if (p < 0) return;
     const int e = ids[p];
     if (e < 0 || e >= E) return;                           // identity expert: nothing to compute
     const int64_t t = p / top;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = threadIdx.x; i < D; i += 128) hs[i] = to_f32<T>(h[t * ldh + i]);
+    const bool vec = rows_vectorise<T>(w_gu, D, D);
+    for (int i = threadIdx.x; i < D; i += 128) hs[staged_at<T>(i, D, vec)] = to_f32<T>(h[t * ldh + i]);
     __syncthreads();
     const T* wg = w_gu + (int64_t)e * 2 * ff * D;           // [gate rows | up rows][D]
     const int j1 = min(ff, (int)(blockIdx.y + 1) * kGuRows);
     for (int j = blockIdx.y * kGuRows + warp; j < j1; j += 4) {
-        float a = row_dot<T>(wg + (int64_t)j * D, hs, D, lane), b = row_dot<T>(wg + (int64_t)(ff + j) * D, hs, D, lane);
+        float a = row_dot<T>(wg + (int64_t)j * D, hs, D, lane, vec), b = row_dot<T>(wg + (int64_t)(ff + j) * D, hs, D, lane, vec);
         a = warp_sum(a); b = warp_sum(b);
         if (lane == 0) act[p * ff + j] = from_f32<T>(a / (1.0f + expf(-a)) * b);
     }
 }
 
+// y[row] = W_down[e] act[p] for the pair p = order[row] (rows in expert order), f32 out
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_down_combine_kernel(const T* __restrict__ act, const T* __restrict__ w_d, const int32_t* __restrict__ ids, const float* __restrict__ weights,
-                        const float* __restrict__ x, int64_t ldx, float* __restrict__ out, int top, int E, int ff, int D) {
+moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_d, const int32_t* __restrict__ ids, const int32_t* __restrict__ order, float* __restrict__ y,
+                int E, int ff, int D) {
     pdl_wait();
     pdl_trigger();
-    extern __shared__ float as[];                          // [top][ff]
-    const int64_t t = blockIdx.x;
+    extern __shared__ float as[];                          // [ff]
+    const int64_t row = blockIdx.x;
+    const int64_t p = order[row];
+    if (p < 0) return;
+    const int e = ids[p];
+    if (e < 0 || e >= E) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int k = 0; k < top; ++k) {
-        const int e = ids[t * top + k];
-        if (e >= 0 && e < E)
-            for (int i = threadIdx.x; i < ff; i += 256) as[k * ff + i] = to_f32<T>(act[(t * top + k) * ff + i]);
-    }
+    const bool vec = rows_vectorise<T>(w_d, ff, ff);
+    for (int i = threadIdx.x; i < ff; i += 256) as[staged_at<T>(i, ff, vec)] = to_f32<T>(act[p * ff + i]);
     __syncthreads();
     const int d1 = min(D, (int)(blockIdx.y + 1) * kDownCols);
     for (int d = blockIdx.y * kDownCols + warp; d < d1; d += 8) {
-        float tot = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int e = ids[t * top + k];
-            const float wk = weights[t * top + k];
-            if (e >= 0 && e < E) {
-                const float a = row_dot<T>(w_d + ((int64_t)e * D + d) * ff, as + k * ff, ff, lane);
-                tot = fmaf(wk, warp_sum(a), tot);
-            } else {
-                tot = fmaf(wk, x[t * ldx + d], tot);
-            }
-        }
-        if (lane == 0) out[t * D + d] = tot;
+        const float a = warp_sum(row_dot<T>(w_d + ((int64_t)e * D + d) * ff, as, ff, lane, vec));
+        if (lane == 0) y[row * D + d] = a;
     }
 }
 
@@ -267,25 +274,23 @@ void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_
     check_launch("moe_gate_up");
 }
 
-void moe_down_combine(const void* act, const void* w_down, const int32_t* ids, const float* weights, const float* x, int64_t ldx, float* out,
-                      int32_t num_tokens, int32_t top, int32_t num_experts, int32_t ff, int32_t width, int32_t dtype, int64_t stream) {
-    if (num_tokens == 0) return;
-    B200_REQUIRE(ids && weights && x && out && top > 0 && width > 0 && ldx >= width && (num_experts == 0 || (act && w_down && ff > 0)), kErrBadArg,
-                 "moe_down_combine: bad arguments");
+void moe_down(const void* act, const void* w_down, const int32_t* ids, const int32_t* order, float* y, int32_t rows, int32_t num_experts, int32_t ff, int32_t width,
+              int32_t dtype, int64_t stream) {
+    if (rows == 0 || num_experts == 0) return;
+    B200_REQUIRE(act && w_down && ids && order && y && ff > 0 && ff <= 40960 && width > 0, kErrBadArg, "moe_down: bad arguments");
     cudaStream_t st = as_stream(stream);
-    const size_t smem = (size_t)top * (ff > 0 ? ff : 1) * sizeof(float);
-    B200_REQUIRE(smem <= 160 * 1024, kErrUnsupported, "moe_down_combine: top * ff = %d floats do not fit shared memory", top * ff);
+    const size_t smem = (size_t)ff * sizeof(float);
+    const dim3 grid(rows, (width + kDownCols - 1) / kDownCols);
     if (dtype == B200_F32) {
-        ensure_dynamic_smem(reinterpret_cast<const void*>(moe_down_combine_kernel<float>), (int)smem);
-        launch_pdl(moe_down_combine_kernel<float>, dim3(num_tokens, (width + kDownCols - 1) / kDownCols), dim3(256), smem, st, (const float*)act, (const float*)w_down, ids, weights, x, ldx, out, top,
-                   num_experts, ff, width);
+        ensure_dynamic_smem(reinterpret_cast<const void*>(moe_down_kernel<float>), (int)smem);
+        launch_pdl(moe_down_kernel<float>, grid, dim3(256), smem, st, (const float*)act, (const float*)w_down, ids, order, y, num_experts, ff, width);
     } else if (dtype == B200_BF16) {
-        ensure_dynamic_smem(reinterpret_cast<const void*>(moe_down_combine_kernel<__nv_bfloat16>), (int)smem);
-        launch_pdl(moe_down_combine_kernel<__nv_bfloat16>, dim3(num_tokens, (width + kDownCols - 1) / kDownCols), dim3(256), smem, st, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, ids,
-                   weights, x, ldx, out, top, num_experts, ff, width);
-    } else { set_error(kErrUnsupported, "moe_down_combine: dtype %d (f32 / bf16)", dtype); return; }
+        ensure_dynamic_smem(reinterpret_cast<const void*>(moe_down_kernel<__nv_bfloat16>), (int)smem);
+        launch_pdl(moe_down_kernel<__nv_bfloat16>, grid, dim3(256), smem, st, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, ids, order, y, num_experts, ff,
+                   width);
+    } else { set_error(kErrUnsupported, "moe_down: dtype %d (f32 / bf16)", dtype); return; }
     count_launch();
-    check_launch("moe_down_combine");
+    check_launch("moe_down");
 }
 
 int64_t moe_align_rows(int64_t pairs, int32_t num_experts, int32_t tile) {

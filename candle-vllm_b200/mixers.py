@@ -142,7 +142,8 @@ class GatedMlp:
         return ops.linear(ops.gelu_tanh_mul(ops.linear(h, self.w_in), self.dtype), self.w_down)
 
 
-GROUPED_MIN_ROWS = 256        # rows (tokens, or token-choice pairs) from which the grouped tensor-core products replace the streaming kernels
+GROUPED_MIN_ROWS = 256        # token-choice pairs from which the grouped tensor-core products replace the streaming expert kernels
+GROUPED_MIN_TOKENS = 16       # rows from which the latent up-projections run head by head on the tensor-core GEMM (each head's rows padded to 128)
 
 
 class LatentAttentionMixer:
@@ -209,7 +210,7 @@ class LatentAttentionMixer:
             ops.latent_kv_rope_cache(proj, self.off_dkv, self.c_norm, self.cos, self.sin, batch, c_cache, kr_cache, self.R, self.dr, self.eps)
         gate = proj[:, self.off_g:] if self.has_gate else None
         T = proj.shape[0]
-        if self.grouped and T >= GROUPED_MIN_ROWS:
+        if self.grouped and T >= GROUPED_MIN_TOKENS:
             # head-major buffers, every head's rows padded to whole 128-row tiles; tile i belongs to head i // (tiles per head)
             Tp = -(-T // 128) * 128
             if Tp not in self._tile_heads:
@@ -270,12 +271,12 @@ class RoutedExperts:
             act = ops.silu_mul_packed(gu, torch.bfloat16)
             y = ops.linear_grouped(act, self.w_d, tile_expert, torch.empty((xg.shape[0], self.w_d.shape[1]), dtype=torch.float32, device=h.device))
             return ops.moe_combine_rows(y, pair_row, wts, x)
-        act = None
-        if self.E:
-            # several tokens: the blocks walk the pairs expert by expert, so that those running together read the same weights
-            order = ops.moe_sorted_rows(ids, self.E, tile=1)[1] if h.shape[0] > 1 else None
-            act = ops.moe_gate_up(h, self.w_gu, ids, order)
-        return ops.moe_down_combine(act, self.w_d, ids, wts, x, self.E, self.ff)
+        if not self.E:                                       # identity experts only
+            return ops.moe_combine_rows(x, torch.full((ids.numel(),), -1, dtype=torch.int32, device=ids.device), wts, x)
+        # few rows: every pair streams its expert; the blocks walk the pairs expert by expert, so that those running together read the same weights
+        pair_row, order, _ = ops.moe_sorted_rows(ids, self.E, tile=1)
+        act = ops.moe_gate_up(h, self.w_gu, ids, order)
+        return ops.moe_combine_rows(ops.moe_down(act, self.w_d, ids, order), pair_row, wts, x)
 
 
 class TokenSideInput:

@@ -296,10 +296,21 @@ def latent_q_absorb(proj: torch.Tensor, w_uk: Optional[torch.Tensor], cos: Optio
     return q_lat
 
 
+LATENT_SPLIT_BLOCKS = 296      # two blocks per SM: steps with fewer (token, head group) blocks cut the keys of every row into runs
+
+
 def latent_attention_varlen(q_lat: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor, batch: StepBatch, sink: Optional[torch.Tensor], heads: int,
-                            rank: int, rot_dim: int, block_size: int, scale: float, window: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q_lat f32 [T, H, rank + rot_dim] (any token / head strides) -> o f32 [T, H, rank], or into ``out`` (f32 or bf16, any token / head strides)"""
+                            rank: int, rot_dim: int, block_size: int, scale: float, window: int = 0, out: Optional[torch.Tensor] = None,
+                            splits: Optional[int] = None) -> torch.Tensor:
+    """q_lat f32 [T, H, rank + rot_dim] (any token / head strides) -> o f32 [T, H, rank], or into ``out`` (f32 or bf16, any token / head strides).
+    ``splits``: runs every row's keys are cut into (None: enough blocks to fill the device when the step has few rows, from the table width, so that
+    a captured step keeps its choice)."""
     T = q_lat.shape[0]
+    if splits is None:
+        blocks = T * -(-heads // (8 if heads >= 8 else 4))
+        longest = batch.block_tables.shape[1] * block_size if window <= 0 else min(window, batch.block_tables.shape[1] * block_size)
+        splits = max(1, min(-(-LATENT_SPLIT_BLOCKS // blocks), longest // 128, 64)) if blocks < LATENT_SPLIT_BLOCKS else 1
+    part = torch.empty((T * heads * splits * (rank + 2),), dtype=torch.float32, device=q_lat.device) if splits > 1 else None
     if out is None:
         out = torch.empty((T, heads, rank), dtype=torch.float32, device=q_lat.device)
     if q_lat.stride(2) != 1 or out.stride(2) != 1:
@@ -307,7 +318,8 @@ def latent_attention_varlen(q_lat: torch.Tensor, c_cache: torch.Tensor, kr_cache
     lib().latent_attention_varlen(_ptr(out), C.c_int64(out.stride(0)), C.c_int64(out.stride(1)), C.c_int32(_tag(out.dtype)), _ptr(q_lat), C.c_int64(q_lat.stride(0)),
                                   C.c_int64(q_lat.stride(1)), _ptr(c_cache), _ptr(kr_cache), _ptr(batch.block_tables), C.c_int32(batch.block_tables.shape[1]),
                                   _ptr(batch.token_seq), _ptr(batch.positions), _ptr(sink), C.c_int32(T), C.c_int32(heads), C.c_int32(rank), C.c_int32(rot_dim),
-                                  C.c_int32(block_size), C.c_float(scale), C.c_int32(window), C.c_int32(_tag(c_cache.dtype)), _stream(q_lat.device))
+                                  C.c_int32(block_size), C.c_float(scale), C.c_int32(window), C.c_int32(_tag(c_cache.dtype)), C.c_int32(splits), _ptr(part),
+                                  _stream(q_lat.device))
     check("latent_attention_varlen")
     return out
 
@@ -364,17 +376,15 @@ def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor, ord
     return act
 
 
-def moe_down_combine(act: Optional[torch.Tensor], w_down: Optional[torch.Tensor], ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, num_experts: int,
-                     ff: int) -> torch.Tensor:
-    """-> f32 [T, D]: the weighted sum of the chosen experts' outputs, identity choices contributing weight * x"""
-    T, D = x.shape
-    top = ids.shape[1]
-    out = torch.empty((T, D), dtype=torch.float32, device=x.device)
-    dt = _tag(w_down.dtype) if w_down is not None else DType.F32
-    lib().moe_down_combine(_ptr(act), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(x), C.c_int64(x.stride(0) if T > 1 else max(D, x.stride(0))), _ptr(out), C.c_int32(T),
-                           C.c_int32(top), C.c_int32(num_experts), C.c_int32(ff), C.c_int32(D), C.c_int32(dt), _stream(x.device))
-    check("moe_down_combine")
-    return out
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, order: torch.Tensor) -> torch.Tensor:
+    """y f32 [rows, D]: y[r] = w_down[e] act[order[r]] for the pairs in the order given (rows of padding or identity choices stay unwritten)"""
+    E, D, ff = w_down.shape
+    rows = order.shape[0]
+    y = torch.empty((rows, D), dtype=torch.float32, device=act.device)
+    lib().moe_down(_ptr(act), _ptr(w_down), _ptr(ids), _ptr(order), _ptr(y), C.c_int32(rows), C.c_int32(E), C.c_int32(ff), C.c_int32(D), C.c_int32(_tag(w_down.dtype)),
+                   _stream(act.device))
+    check("moe_down")
+    return y
 
 
 def moe_sorted_rows(ids: torch.Tensor, num_experts: int, tile: int = 128):

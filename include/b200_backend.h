@@ -490,6 +490,7 @@ void b200_allreduce_f32(void* nccl_comm, float* buf, int64_t n, int64_t stream);
  *   w_dtype; w_uk null = only the rotated part is written.
  * latent_attention_varlen: o_lat f32 [T, H, rank] = sum_j p_j c_j over the keys j <= positions[t] (and positions[t] - j < window when window > 0) of the
  *   token's sequence, p = softmax of (q_lat . (c_j | kr_j)) * scale whose denominator also holds exp(sink[h]) (sink f32 [H] or null).  rank <= 1024.
+ *   splits > 1 cuts every row's keys into that many runs folded by a second kernel; partials = f32 [T, H, splits, rank + 2] scratch.
  * latent_out_gate: out [T, H, dv] = sigmoid(gate[t, h]) * (w_uv[h] src[t, h]), w_uv [H dv, rank], src f32 [T, H, rank]; w_uv null: src is f32
  *   [T, H, dv] already; gate f32 (row pitch ld_gate) or null.
  * moe_route: logits f32 [T, N] -> ids i32 [T, top], weights f32 [T, top]: softmax over N; choice = softmax + correction (f32 [N] or null); only
@@ -497,8 +498,8 @@ void b200_allreduce_f32(void* nccl_comm, float* buf, int64_t n, int64_t stream);
  *   taken / (their sum + 1e-20) * scale.  groups <= 1: no restriction.
  * moe_gate_up: act [T top, ff] = silu(W_gate[e] h_t) * (W_up[e] h_t) for every pair with e = ids[p] < num_experts; w_gate_up [E, 2 ff, width]; order
  *   (i32 [T top] or null) = the pairs in the order the blocks take them (negative = none), e.g. row_pair of moe_align with tile 1.
- * moe_down_combine: out f32 [T, width] = sum_k weights[t, k] * (W_down[e] act[t, k]) (e < num_experts) or weights[t, k] * x[t] (identity expert);
- *   w_down [E, width, ff]. */
+ * moe_down: y f32 [rows, width]: y[r] = W_down[e] act[p] for p = order[r] >= 0, e = ids[p] < num_experts; w_down [E, width, ff]; moe_combine_rows then
+ *   adds every token's choices. */
 void embedding_bigram(const void* table, const void* bigram, const int32_t* ids, const int32_t* positions, const int32_t* token_seq,
                       const int32_t* cu_seqlens, const int32_t* seq_slots, int32_t* prev_state, float* out, int32_t num_tokens, int32_t dim,
                       int32_t vocab, int32_t buckets, int32_t mul_prev, int32_t mul_cur, int32_t table_dtype, int64_t stream);
@@ -515,7 +516,8 @@ void latent_q_absorb(const float* proj, int64_t ld, const void* w_uk, const floa
 void latent_attention_varlen(void* o_lat, int64_t o_stride_token, int64_t o_stride_head, int32_t out_dtype, const float* q_lat, int64_t q_stride_token,
                              int64_t q_stride_head, const void* c_cache, const void* kr_cache, const int32_t* block_tables, int32_t table_width,
                              const int32_t* token_seq, const int32_t* positions, const float* sink, int32_t num_tokens, int32_t num_heads, int32_t rank,
-                             int32_t rot_dim, int32_t block_size, float scale, int32_t window, int32_t cache_dtype, int64_t stream);
+                             int32_t rot_dim, int32_t block_size, float scale, int32_t window, int32_t cache_dtype, int32_t splits, float* partials,
+                             int64_t stream);
 void latent_out_gate(const float* src, int64_t src_stride_token, int64_t src_stride_head, const void* w_uv, const float* gate, int64_t ld_gate, void* out,
                      int32_t num_tokens, int32_t num_heads, int32_t dv, int32_t rank, int32_t w_dtype, int32_t out_dtype, int64_t stream);
 /* linear_grouped: out[r, :n] (out_dtype F32 / BF16, row pitch ldy) = x[r, :k] . weight[tile_group[r / 128]]^T: bf16 x [m_pad, k] (row pitch ldx, m_pad a
@@ -540,8 +542,8 @@ void moe_route(const float* logits, int64_t ld, const float* correction, int32_t
                int32_t groups, int32_t keep, float scale, int64_t stream);
 void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, const int32_t* order, void* act, int32_t num_tokens, int32_t top,
                  int32_t num_experts, int32_t ff, int32_t width, int32_t dtype, int64_t stream);
-void moe_down_combine(const void* act, const void* w_down, const int32_t* ids, const float* weights, const float* x, int64_t ldx, float* out,
-                      int32_t num_tokens, int32_t top, int32_t num_experts, int32_t ff, int32_t width, int32_t dtype, int64_t stream);
+void moe_down(const void* act, const void* w_down, const int32_t* ids, const int32_t* order, float* y, int32_t rows, int32_t num_experts, int32_t ff, int32_t width,
+              int32_t dtype, int64_t stream);
 
 #ifdef __cplusplus
 }
