@@ -14,7 +14,6 @@ import sys
 def _generate(argv) -> int:
     import torch
     from ._lib import ensure_built
-    ensure_built("ragged")
     from .engine import LLMEngine
     from .sampling import SamplingParams
     ap = argparse.ArgumentParser(prog="generate")
@@ -31,6 +30,8 @@ def _generate(argv) -> int:
     ap.add_argument("--prefill-chunk", type=int, default=512)
     ap.add_argument("--decode-graphs", action="store_true", help="replay captured CUDA graphs for steps of single tokens")
     a = ap.parse_args(argv)
+    from .registry import build_group_of
+    ensure_built(build_group_of(a.model))
     prompts = [[int(t) for t in p.split(",") if t.strip()] for p in a.prompt_ids]
     eng = LLMEngine.from_pretrained(a.model, dtype=torch.bfloat16 if a.dtype == "bfloat16" else torch.float32, num_blocks=a.num_blocks,
                                     max_num_seqs=a.max_num_seqs, prefill_chunk=a.prefill_chunk, decode_graphs=a.decode_graphs,

@@ -36,18 +36,20 @@ SYMBOLS = [
     "gemm_half_q_half_alt", "b200_set_scratch",
     "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled", "causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_delta_rule_step", "gated_rms_norm",
     "qk_norm_rope_cache", "paged_attention_varlen", "chunk_decode_view",
-    "embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows",
+    "embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink", "repack_heads", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows",
 ]
 
 
 # what a library built from one source group (build.GROUPS) exports
+_COMMON = ["b200_abi_version", "b200_last_error", "b200_last_error_message", "b200_device_sm_count", "b200_device_cc", "b200_total_kernel_launches", "linear_16bit",
+           "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled", "argmax_f32", "rms_norm", "cast"]
 GROUP_SYMBOLS = {
-    "ragged": ["b200_abi_version", "b200_last_error", "b200_last_error_message", "b200_device_sm_count", "b200_device_cc",
-               "b200_total_kernel_launches", "linear_16bit", "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled",
-               "causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_delta_rule_step", "gated_rms_norm", "qk_norm_rope_cache", "paged_attention_varlen", "chunk_decode_view",
-               "paged_attention_decode", "paged_attention_decode_workspace_bytes", "argmax_f32",
-               "rms_norm", "cast",
-               "embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows"],
+    "ragged": _COMMON + ["causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_delta_rule_step", "gated_rms_norm", "qk_norm_rope_cache",
+                         "paged_attention_varlen", "chunk_decode_view", "paged_attention_decode", "paged_attention_decode_workspace_bytes"],
+    "latent": _COMMON + ["embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen",
+                         "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink",
+                         "mla_paged_decode_workspace_bytes", "repack_heads", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed",
+                         "moe_combine_rows"],
 }
 _RESTYPES = {"b200_last_error_message": C.c_char_p, "paged_attention_decode_workspace_bytes": C.c_size_t, "qmatmul_workspace_bytes": C.c_size_t,
              "moe_gemm_workspace_bytes": C.c_size_t, "moe_gemm_fp8_workspace_bytes": C.c_size_t, "mla_paged_decode_workspace_bytes": C.c_size_t,
@@ -79,7 +81,7 @@ def lib() -> C.CDLL:
 
 def ensure_built(group: str) -> C.CDLL:
     """For programs that start from a source-only checkout: use the full library when it is there, otherwise compile (once) and load the
-    library of ``group`` alone -- the kernels one model family needs."""
+    library of ``group`` alone -- the kernels one model family needs (``registry.build_group_of`` names the group of a checkpoint)."""
     global _lib
     if _lib is None and not os.path.exists(_SO):
         import importlib.util

@@ -35,7 +35,10 @@ def _newer(target: str, deps) -> bool:
 # compiles that and nothing else.  "ragged" = the ragged-step decoders (seq_ops.py): error state, both linear kernels, norms /
 # activations, recurrent, attention and latent-attention mixers, routed experts, argmax.
 GROUPS = {"ragged": ["lib", "linear_generic", "dense_gemm", "norm_act", "gated_delta", "attention_varlen", "attention_prefill", "attention_decode", "attention_generic",
-                     "attention_api", "elementwise", "latent_attention", "moe_ragged"]}
+                     "attention_api", "elementwise"],
+          # latent attention + routed experts: both linear kernels (the tcgen05 one also in its grouped form), norms, the latent mixers incl. the
+          # split-KV latent decode kernel, the expert kernels, argmax
+          "latent": ["lib", "linear_generic", "dense_gemm", "norm_act", "latent_attention", "moe_ragged", "mla", "elementwise"]}
 
 
 def so_path(group=None) -> str:

@@ -249,6 +249,21 @@ latent_out_gate_kernel(const float* __restrict__ src, int64_t s_st, int64_t s_sh
     }
 }
 
+// out[t, h, :n] (bf16, any token / head strides) = src[t, h, :n] (f32 or bf16, any strides): moves rows between the head-major buffers of the grouped
+// products and the token-major ones of the split-KV decode kernel; optionally also ctx[t] = positions[t] + 1
+template <typename TS>
+__global__ void __launch_bounds__(128)
+repack_heads_kernel(const TS* __restrict__ src, int64_t s_st, int64_t s_sh, __nv_bfloat16* __restrict__ dst, int64_t d_st, int64_t d_sh, int n,
+                    const int32_t* __restrict__ positions, uint32_t* __restrict__ ctx) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const TS* s = src + (int64_t)t * s_st + (int64_t)h * s_sh;
+    __nv_bfloat16* d = dst + (int64_t)t * d_st + (int64_t)h * d_sh;
+    for (int i = threadIdx.x; i < n; i += 128) d[i] = __float2bfloat16_rn(to_f32<TS>(s[i]));
+    if (ctx && h == 0 && threadIdx.x == 0) ctx[t] = (uint32_t)(positions[t] + 1);
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -363,6 +378,23 @@ void latent_out_gate(const float* src, int64_t src_stride_token, int64_t src_str
 #undef LOG
     count_launch();
     check_launch("latent_out_gate");
+}
+
+void repack_heads(const void* src, int32_t src_dtype, int64_t src_stride_token, int64_t src_stride_head, void* dst, int64_t dst_stride_token, int64_t dst_stride_head,
+                  int32_t num_tokens, int32_t num_heads, int32_t n, const int32_t* positions, uint32_t* context_lens, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(src && dst && num_heads > 0 && num_heads <= 65535 && n > 0 && (!context_lens || positions), kErrBadArg, "repack_heads: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    const dim3 grid(num_tokens, num_heads);
+    if (src_dtype == B200_F32)
+        launch_pdl(repack_heads_kernel<float>, grid, dim3(128), 0, st, (const float*)src, src_stride_token, src_stride_head, (__nv_bfloat16*)dst, dst_stride_token,
+                   dst_stride_head, n, positions, context_lens);
+    else if (src_dtype == B200_BF16)
+        launch_pdl(repack_heads_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, (const __nv_bfloat16*)src, src_stride_token, src_stride_head, (__nv_bfloat16*)dst,
+                   dst_stride_token, dst_stride_head, n, positions, context_lens);
+    else { set_error(kErrUnsupported, "repack_heads: source dtype %d (f32 / bf16)", src_dtype); return; }
+    count_launch();
+    check_launch("repack_heads");
 }
 
 }  // extern "C"

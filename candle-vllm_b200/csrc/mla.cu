@@ -259,14 +259,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap cmap, const __grid_constan
 template <typename T>
 __global__ void __launch_bounds__(128)
 mla_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml, const uint32_t* __restrict__ context_lens,
-                 int num_heads, int max_chunks) {
+                 int num_heads, int max_chunks, const float* __restrict__ sink) {
     const int head = blockIdx.x, seq = blockIdx.y;
     const int ctx = (int)context_lens[seq];
     const int nchunks = (ctx + kChunkTok - 1) / kChunkTok;
     const int64_t base = ((int64_t)seq * num_heads + head) * max_chunks;
-    float M = -INFINITY;
+    // a softmax sink (one learned score per head, no key, no value) joins the maximum and the denominator here; the partial maxima are in
+    // log2 units (scores were scaled by log2 e), the sink comes in natural units
+    const float sink2 = sink ? sink[head] * 1.4426950408889634f : -INFINITY;
+    float M = sink2;
     for (int c = 0; c < nchunks; ++c) M = fmaxf(M, part_ml[(base + c) * 2]);
-    float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float L = sink ? exp2f(sink2 - M) : 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c = 0; c < nchunks; ++c) {
         const float w = exp2f(part_ml[(base + c) * 2] - M);
         L += w * part_ml[(base + c) * 2 + 1];
@@ -384,10 +387,23 @@ size_t mla_paged_decode_workspace_bytes(int32_t num_seqs, int32_t num_heads, int
     return (size_t)num_seqs * num_heads * chunks * (kLat * 4 + 8) + 256;
 }
 
+// 1 when mla_paged_attention_sink would run these sizes on the split-KV tensor-core decode kernel (one row per sequence)
+int32_t mla_decode_kernel_supported(int32_t kv_lora_rank, int32_t qk_rope_head_dim, int32_t block_size, int32_t dtype) {
+    return kv_lora_rank == kLat && qk_rope_head_dim == kRope && block_size == kPg && (dtype == B200_BF16 || dtype == B200_F16) ? 1 : 0;
+}
+
 void mla_paged_attention(void* out, const void* q_absorbed, const void* q_pe, const void* ckv_cache, const void* kpe_cache, const uint32_t* block_tables,
                          const uint32_t* context_lens, const uint32_t* cu_seqlens_q, int32_t num_seqs, int32_t num_rows, int32_t num_heads,
                          int32_t kv_lora_rank, int32_t qk_rope_head_dim, int32_t block_size, int32_t max_blocks_per_seq, int64_t num_blocks, float sm_scale,
                          int32_t dtype, void* workspace, size_t workspace_bytes, int64_t stream) {
+    mla_paged_attention_sink(out, q_absorbed, q_pe, ckv_cache, kpe_cache, block_tables, context_lens, cu_seqlens_q, nullptr, num_seqs, num_rows, num_heads, kv_lora_rank,
+                             qk_rope_head_dim, block_size, max_blocks_per_seq, num_blocks, sm_scale, dtype, workspace, workspace_bytes, stream);
+}
+
+void mla_paged_attention_sink(void* out, const void* q_absorbed, const void* q_pe, const void* ckv_cache, const void* kpe_cache, const uint32_t* block_tables,
+                              const uint32_t* context_lens, const uint32_t* cu_seqlens_q, const float* sink, int32_t num_seqs, int32_t num_rows, int32_t num_heads,
+                              int32_t kv_lora_rank, int32_t qk_rope_head_dim, int32_t block_size, int32_t max_blocks_per_seq, int64_t num_blocks, float sm_scale,
+                              int32_t dtype, void* workspace, size_t workspace_bytes, int64_t stream) {
     if (num_rows == 0 || num_seqs == 0) return;
     B200_REQUIRE(out && q_absorbed && q_pe && ckv_cache && kpe_cache && block_tables && context_lens, kErrBadArg, "mla_paged_attention: null pointer");
     B200_REQUIRE(dtype == B200_BF16 || dtype == B200_F16, kErrUnsupported, "mla_paged_attention: dtype %d (f16 / bf16)", dtype);
@@ -409,17 +425,18 @@ void mla_paged_attention(void* out, const void* q_absorbed, const void* q_pe, co
             if (dtype == B200_BF16) {
                 ensure_dynamic_smem(reinterpret_cast<const void*>(mla_decode_kernel<__nv_bfloat16>), kMlaSmem);
                 mla_decode_kernel<__nv_bfloat16><<<grid, 128, kMlaSmem, st>>>(cm, pm, p);
-                mla_merge_kernel<__nv_bfloat16><<<dim3(num_heads, num_seqs), 128, 0, st>>>((__nv_bfloat16*)out, p.part_o, p.part_ml, context_lens, num_heads, max_chunks);
+                mla_merge_kernel<__nv_bfloat16><<<dim3(num_heads, num_seqs), 128, 0, st>>>((__nv_bfloat16*)out, p.part_o, p.part_ml, context_lens, num_heads, max_chunks, sink);
             } else {
                 ensure_dynamic_smem(reinterpret_cast<const void*>(mla_decode_kernel<__half>), kMlaSmem);
                 mla_decode_kernel<__half><<<grid, 128, kMlaSmem, st>>>(cm, pm, p);
-                mla_merge_kernel<__half><<<dim3(num_heads, num_seqs), 128, 0, st>>>((__half*)out, p.part_o, p.part_ml, context_lens, num_heads, max_chunks);
+                mla_merge_kernel<__half><<<dim3(num_heads, num_seqs), 128, 0, st>>>((__half*)out, p.part_o, p.part_ml, context_lens, num_heads, max_chunks, sink);
             }
             count_launch(2);
             check_launch("mla_paged_attention");
             return;
         }
     }
+    B200_REQUIRE(!sink, kErrUnsupported, "mla_paged_attention_sink: a sink needs the split-KV decode kernel (latent 512, rope 64, 64-token blocks, one row per sequence)");
     const dim3 grid(num_heads, num_rows);
     if (dtype == B200_BF16)
         mla_generic_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)q_absorbed, (const __nv_bfloat16*)q_pe, (const __nv_bfloat16*)ckv_cache,

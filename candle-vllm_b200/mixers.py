@@ -189,6 +189,7 @@ class LatentAttentionMixer:
         self.grouped = dtype == torch.bfloat16 and dn % 8 == 0 and rank % 8 == 0 and dn >= 64 and rank >= 64
         self.uk_t = self.w_uk.view(heads, dn, rank).transpose(1, 2).contiguous() if self.grouped else None
         self._tile_heads = {}
+        self.decode_kernel = self.grouped and self.window == 0 and ops.latent_decode_kernel_supported(rank, rot_dim, block_size, dtype)
         self.cos = self.sin = None
         self._device = self.w_in.device
         if rot and rot_dim:
@@ -224,8 +225,15 @@ class LatentAttentionMixer:
             ops.linear_grouped(qn16.view(self.H * Tp, self.dn), self.uk_t, heads_of, q_hm.view(self.H * Tp, self.R + self.dr))
             o16 = torch.zeros((self.H, Tp, self.R), dtype=torch.bfloat16, device=proj.device) if Tp != T else torch.empty((self.H, Tp, self.R), dtype=torch.bfloat16,
                                                                                                                        device=proj.device)
-            ops.latent_attention_varlen(q_lat[:T], c_cache, kr_cache, batch, self.sink, self.H, self.R, self.dr, self.block_size, self.scale, self.window,
-                                        out=o16.transpose(0, 1)[:T])
+            if self.decode_kernel and batch.pure_decode and T <= 65535:
+                # steps of single tokens at the sizes the split-KV tensor-core kernel of the latent cache takes: token-major 16-bit queries in, latents out
+                qa = ops.repack_heads(q_lat[:T, :, :self.R], torch.empty((T, self.H, self.R), dtype=torch.bfloat16, device=proj.device))
+                ctx = torch.empty((T,), dtype=torch.int32, device=proj.device)
+                qr = ops.repack_heads(q_lat[:T, :, self.R:], torch.empty((T, self.H, self.dr), dtype=torch.bfloat16, device=proj.device), batch.positions, ctx)
+                ops.repack_heads(ops.latent_attention_decode(qa, qr, c_cache, kr_cache, batch, ctx, self.sink, self.scale), o16.transpose(0, 1)[:T])
+            else:
+                ops.latent_attention_varlen(q_lat[:T], c_cache, kr_cache, batch, self.sink, self.H, self.R, self.dr, self.block_size, self.scale, self.window,
+                                            out=o16.transpose(0, 1)[:T])
             v_hm = torch.empty((self.H, Tp, self.dv), dtype=torch.float32, device=proj.device)
             ops.linear_grouped(o16.view(self.H * Tp, self.R), self.w_uv.view(self.H, self.dv, self.R), heads_of, v_hm.view(self.H * Tp, self.dv))
             a = ops.latent_out_gate(v_hm.transpose(0, 1)[:T], None, gate, self.H, self.dv, self.R, self.dtype)

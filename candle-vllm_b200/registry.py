@@ -25,6 +25,15 @@ def architecture_of(config: dict) -> str:
     raise BackendError("config.json names no architecture")
 
 
+# the source group (build.GROUPS) whose library alone serves an architecture, for a first start from a source-only checkout
+_BUILD_GROUP = {"Gobesun": "ragged", "Guvusun": "latent"}
+
+
+def build_group_of(path: str) -> str:
+    with open(os.path.join(path, "config.json")) as f:
+        return _BUILD_GROUP.get(architecture_of(json.load(f)), "ragged")
+
+
 def registered() -> list:
     return sorted(_REGISTRY)
 

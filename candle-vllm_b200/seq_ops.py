@@ -425,3 +425,36 @@ def moe_combine_rows(y: torch.Tensor, pair_row: torch.Tensor, weights: torch.Ten
                            C.c_int32(top), C.c_int32(D), _stream(x.device))
     check("moe_combine_rows")
     return out
+
+
+def repack_heads(src: torch.Tensor, dst: torch.Tensor, positions: Optional[torch.Tensor] = None, context_lens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dst[t, h, :] (bf16) = src[t, h, :] (f32 / bf16), each with its own token / head strides; with ``context_lens`` (i32 [T]) also positions + 1"""
+    T, H, n = dst.shape
+    if dst.dtype != torch.bfloat16 or src.shape != dst.shape or src.stride(2) != 1 or dst.stride(2) != 1:
+        raise BackendError("repack_heads: [T, H, n] tensors with a contiguous last axis, bf16 destination")
+    lib().repack_heads(_ptr(src), C.c_int32(_tag(src.dtype)), C.c_int64(src.stride(0)), C.c_int64(src.stride(1)), _ptr(dst), C.c_int64(dst.stride(0)),
+                       C.c_int64(dst.stride(1)), C.c_int32(T), C.c_int32(H), C.c_int32(n), _ptr(positions), _ptr(context_lens), _stream(dst.device))
+    check("repack_heads")
+    return dst
+
+
+def latent_decode_kernel_supported(rank: int, rot_dim: int, block_size: int, dtype: torch.dtype) -> bool:
+    return dtype == torch.bfloat16 and bool(lib().mla_decode_kernel_supported(C.c_int32(rank), C.c_int32(rot_dim), C.c_int32(block_size), C.c_int32(DType.BF16)))
+
+
+def latent_attention_decode(q_abs: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor, batch: StepBatch, context_lens: torch.Tensor,
+                            sink: Optional[torch.Tensor], scale: float) -> torch.Tensor:
+    """A step of single tokens on the split-KV tensor-core kernel of the latent cache (csrc/mla.cu: TMA tiles, 16 heads per MMA, partials folded by a
+    merge kernel that also takes the sink): q_abs bf16 [B, H, 512], q_rot bf16 [B, H, 64], bf16 caches of 64-token blocks -> bf16 [B, H, 512]."""
+    B, H, R = q_abs.shape
+    W = batch.block_tables.shape[1]
+    bs = c_cache.shape[1]
+    out = torch.empty((B, H, R), dtype=torch.bfloat16, device=q_abs.device)
+    L = lib()
+    need = int(L.mla_paged_decode_workspace_bytes(C.c_int32(B), C.c_int32(H), C.c_int32(W), C.c_int32(bs)))
+    ws = torch.empty(need, dtype=torch.uint8, device=q_abs.device)
+    L.mla_paged_attention_sink(_ptr(out), _ptr(q_abs), _ptr(q_rot), _ptr(c_cache), _ptr(kr_cache), _ptr(batch.block_tables), _ptr(context_lens), _ptr(None), _ptr(sink),
+                               C.c_int32(B), C.c_int32(B), C.c_int32(H), C.c_int32(R), C.c_int32(q_rot.shape[2]), C.c_int32(bs), C.c_int32(W), C.c_int64(c_cache.shape[0]),
+                               C.c_float(scale), C.c_int32(DType.BF16), _ptr(ws), C.c_size_t(need), _stream(q_abs.device))
+    check("latent_attention_decode")
+    return out

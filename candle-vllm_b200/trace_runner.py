@@ -31,7 +31,8 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
 
     from ._lib import ensure_built
-    ensure_built("ragged")
+    from .registry import build_group_of
+    ensure_built(build_group_of(a.model))
     from .engine import ModelRunner
     from .registry import load_model
     torch.cuda.set_device(0)

@@ -520,6 +520,17 @@ void latent_attention_varlen(void* o_lat, int64_t o_stride_token, int64_t o_stri
                              int64_t stream);
 void latent_out_gate(const float* src, int64_t src_stride_token, int64_t src_stride_head, const void* w_uv, const float* gate, int64_t ld_gate, void* out,
                      int32_t num_tokens, int32_t num_heads, int32_t dv, int32_t rank, int32_t w_dtype, int32_t out_dtype, int64_t stream);
+/* mla_paged_attention_sink: mla_paged_attention with a softmax sink: sink f32 [H] (or null) adds exp(sink[h]) to every denominator of head h; only on the
+ *   split-KV decode kernel (mla_decode_kernel_supported(...) == 1, one row per sequence).
+ * repack_heads: dst[t, h, :n] (bf16) = src[t, h, :n] (F32 / BF16), both with their own token / head strides (elements); with context_lens (u32 [T]) also
+ *   context_lens[t] = positions[t] + 1. */
+int32_t mla_decode_kernel_supported(int32_t kv_lora_rank, int32_t qk_rope_head_dim, int32_t block_size, int32_t dtype);
+void mla_paged_attention_sink(void* out, const void* q_absorbed, const void* q_pe, const void* ckv_cache, const void* kpe_cache, const uint32_t* block_tables,
+                              const uint32_t* context_lens, const uint32_t* cu_seqlens_q, const float* sink, int32_t num_seqs, int32_t num_rows, int32_t num_heads,
+                              int32_t kv_lora_rank, int32_t qk_rope_head_dim, int32_t block_size, int32_t max_blocks_per_seq, int64_t num_blocks, float sm_scale,
+                              int32_t dtype, void* workspace, size_t workspace_bytes, int64_t stream);
+void repack_heads(const void* src, int32_t src_dtype, int64_t src_stride_token, int64_t src_stride_head, void* dst, int64_t dst_stride_token, int64_t dst_stride_head,
+                  int32_t num_tokens, int32_t num_heads, int32_t n, const int32_t* positions, uint32_t* context_lens, int64_t stream);
 /* linear_grouped: out[r, :n] (out_dtype F32 / BF16, row pitch ldy) = x[r, :k] . weight[tile_group[r / 128]]^T: bf16 x [m_pad, k] (row pitch ldx, m_pad a
  *   multiple of 128) whose rows come in tiles of 128 that each multiply one matrix of the bf16 stack weight [groups, n, k]; tile_group i32 [m_pad / 128] on
  *   the device, a negative entry skips the tile.  The tcgen05 GEMM of linear_16bit with the weight tile chosen per row tile.

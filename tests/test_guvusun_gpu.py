@@ -482,6 +482,37 @@ def test_many_rows_take_the_tensor_core_routes():
     assert float(e.median()) < 0.03
 
 
+def test_single_token_steps_on_the_split_kv_latent_kernel():
+    """latent 512 + rotated 64 in bf16 with 64-token blocks: steps of 16 and more single tokens run on the split-KV tensor-core kernel of the latent
+    cache, whose merge takes the sink; contexts on both sides of its 256-key runs and of block borders, scattered blocks, decoded side by side"""
+    cfg = S.guvusun_config(128, 150, [S.guvusun_layer(4, 64, 64, 32, 512, experts=4, ff=64, top=2, identity=1, scaling=YARN),
+                                      S.guvusun_layer(3, 64, 64, 40, 512, kv_from=0, scaling=YARN)], bigram=dict(buckets=31, mul_prev=7, mul_cur=3))
+    w = S.guvusun_weights(cfg, 5)
+    w["l0.mix.sink"] = torch.tensor([4.0, -2.0, 1.0, 7.0]).to(torch.bfloat16)          # sinks that visibly take weight
+    model = GuvusunModel(GuvusunConfig.from_dict(cfg), w, dtype=torch.bfloat16, block_size=64, max_pos=512, device=DEV)
+    assert model.layers[0].mixer.decode_kernel and model.layers[1].mixer.decode_kernel
+    g = torch.Generator().manual_seed(6)
+    lens = [1, 2, 63, 64, 65, 127, 128, 129, 250, 255, 256, 257, 300, 17, 200, 90, 5]
+    steps = 4
+    seqs = [torch.randint(0, 150, (n + steps,), generator=g).tolist() for n in lens]
+    refs = [G.forward(cfg, w, s) for s in seqs]
+    runner = ModelRunner(model, 60, len(lens), 64)
+    got = [[] for _ in lens]
+    for i in reversed(range(len(lens))):                                                # admitted in reverse: tables are not in sequence order
+        runner.admit(i)
+        runner.execute([dict(seq_id=i, tokens=seqs[i][:lens[i]], want=[])])
+    for k in range(steps):
+        out = runner.execute([dict(seq_id=i, tokens=[seqs[i][lens[i] + k]], want=[0]) for i in range(len(lens))])
+        for i in range(len(lens)):
+            got[i].append(out[i:i + 1])
+    errs = torch.cat([row_errors(torch.cat(got[i]), refs[i][lens[i]:]) for i in range(len(lens))])
+    assert float(errs.median()) < 0.03 and float(errs.quantile(0.9)) < 0.08 and float(errs.max()) < 0.3, (float(errs.median()), float(errs.max()))
+    # without the sink the same rows move by far more than rounding: the merge does take it
+    w2 = dict(w); w2["l0.mix.sink"] = torch.full((4,), -30.0).to(torch.bfloat16)
+    other = torch.cat([row_errors(torch.cat(got[i]), G.forward(cfg, w2, seqs[i])[lens[i]:]) for i in (3, 8)])
+    assert float(other.median()) > 3 * float(errs.median())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_greedy_generation_through_the_engine(dtype, tmp_path):
     """checkpoint on disk -> registry -> LLMEngine (scheduler, chunked prefill, sampler) against the oracle's greedy continuation"""
