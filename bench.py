@@ -929,7 +929,7 @@ def run_guvusun(args):
         kern = {}
         names = ["linear", "linear_grouped", "rms_norm_ex", "residual_rms_norm", "embedding_bigram", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb",
                  "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "moe_sorted_rows", "moe_gather_rows", "silu_mul_packed",
-                 "moe_combine_rows"]
+                 "moe_combine_rows", "repack_heads", "latent_attention_decode"]
         orig = {n: getattr(ops, n) for n in names}
 
         def instrument(tag):

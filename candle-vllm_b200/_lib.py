@@ -36,7 +36,7 @@ SYMBOLS = [
     "gemm_half_q_half_alt", "b200_set_scratch",
     "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled", "causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_delta_rule_step", "gated_rms_norm",
     "qk_norm_rope_cache", "paged_attention_varlen", "chunk_decode_view",
-    "embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink", "repack_heads", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows",
+    "embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink", "repack_heads", "token_tables", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows",
 ]
 
 
@@ -48,7 +48,7 @@ GROUP_SYMBOLS = {
                          "paged_attention_varlen", "chunk_decode_view", "paged_attention_decode", "paged_attention_decode_workspace_bytes"],
     "latent": _COMMON + ["embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen",
                          "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink",
-                         "mla_paged_decode_workspace_bytes", "repack_heads", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed",
+                         "mla_paged_decode_workspace_bytes", "repack_heads", "token_tables", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed",
                          "moe_combine_rows"],
 }
 _RESTYPES = {"b200_last_error_message": C.c_char_p, "paged_attention_decode_workspace_bytes": C.c_size_t, "qmatmul_workspace_bytes": C.c_size_t,

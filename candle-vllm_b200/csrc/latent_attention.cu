@@ -264,6 +264,19 @@ repack_heads_kernel(const TS* __restrict__ src, int64_t s_st, int64_t s_sh, __nv
     if (ctx && h == 0 && threadIdx.x == 0) ctx[t] = (uint32_t)(positions[t] + 1);
 }
 
+// every row of a step as a one-row "sequence": its own copy of its sequence's block table and its context length (position + 1), the form in
+// which the split-KV decode kernel serves rows of prompts as well
+__global__ void __launch_bounds__(64)
+token_tables_kernel(const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ token_seq, const int32_t* __restrict__ positions,
+                    uint32_t* __restrict__ out_tables, uint32_t* __restrict__ ctx) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t t = blockIdx.x;
+    const int32_t* src = block_tables + (int64_t)token_seq[t] * table_width;
+    for (int i = threadIdx.x; i < table_width; i += 64) out_tables[t * table_width + i] = (uint32_t)src[i];
+    if (threadIdx.x == 0) ctx[t] = (uint32_t)(positions[t] + 1);
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -395,6 +408,15 @@ void repack_heads(const void* src, int32_t src_dtype, int64_t src_stride_token, 
     else { set_error(kErrUnsupported, "repack_heads: source dtype %d (f32 / bf16)", src_dtype); return; }
     count_launch();
     check_launch("repack_heads");
+}
+
+void token_tables(const int32_t* block_tables, int32_t table_width, const int32_t* token_seq, const int32_t* positions, uint32_t* out_tables,
+                  uint32_t* context_lens, int32_t num_tokens, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(block_tables && token_seq && positions && out_tables && context_lens && table_width > 0, kErrBadArg, "token_tables: bad arguments");
+    launch_pdl(token_tables_kernel, dim3(num_tokens), dim3(64), 0, as_stream(stream), block_tables, table_width, token_seq, positions, out_tables, context_lens);
+    count_launch();
+    check_launch("token_tables");
 }
 
 }  // extern "C"

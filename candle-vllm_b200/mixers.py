@@ -225,12 +225,13 @@ class LatentAttentionMixer:
             ops.linear_grouped(qn16.view(self.H * Tp, self.dn), self.uk_t, heads_of, q_hm.view(self.H * Tp, self.R + self.dr))
             o16 = torch.zeros((self.H, Tp, self.R), dtype=torch.bfloat16, device=proj.device) if Tp != T else torch.empty((self.H, Tp, self.R), dtype=torch.bfloat16,
                                                                                                                        device=proj.device)
-            if self.decode_kernel and batch.pure_decode and T <= 65535:
-                # steps of single tokens at the sizes the split-KV tensor-core kernel of the latent cache takes: token-major 16-bit queries in, latents out
+            if self.decode_kernel:
+                # the sizes the split-KV tensor-core kernel of the latent cache takes: every row (a decoded token or a row of a prompt) goes in as a
+                # one-row sequence with its own context length; token-major 16-bit queries in, latents out
                 qa = ops.repack_heads(q_lat[:T, :, :self.R], torch.empty((T, self.H, self.R), dtype=torch.bfloat16, device=proj.device))
-                ctx = torch.empty((T,), dtype=torch.int32, device=proj.device)
-                qr = ops.repack_heads(q_lat[:T, :, self.R:], torch.empty((T, self.H, self.dr), dtype=torch.bfloat16, device=proj.device), batch.positions, ctx)
-                ops.repack_heads(ops.latent_attention_decode(qa, qr, c_cache, kr_cache, batch, ctx, self.sink, self.scale), o16.transpose(0, 1)[:T])
+                qr = ops.repack_heads(q_lat[:T, :, self.R:], torch.empty((T, self.H, self.dr), dtype=torch.bfloat16, device=proj.device))
+                tables, ctx = ops.token_tables(batch)
+                ops.repack_heads(ops.latent_attention_decode(qa, qr, c_cache, kr_cache, tables, ctx, self.sink, self.scale), o16.transpose(0, 1)[:T])
             else:
                 ops.latent_attention_varlen(q_lat[:T], c_cache, kr_cache, batch, self.sink, self.H, self.R, self.dr, self.block_size, self.scale, self.window,
                                             out=o16.transpose(0, 1)[:T])

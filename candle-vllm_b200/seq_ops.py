@@ -442,19 +442,38 @@ def latent_decode_kernel_supported(rank: int, rot_dim: int, block_size: int, dty
     return dtype == torch.bfloat16 and bool(lib().mla_decode_kernel_supported(C.c_int32(rank), C.c_int32(rot_dim), C.c_int32(block_size), C.c_int32(DType.BF16)))
 
 
-def latent_attention_decode(q_abs: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor, batch: StepBatch, context_lens: torch.Tensor,
+def token_tables(batch: StepBatch):
+    """-> (tables i32 [T, W], context_lens i32 [T]): every row of the step with its sequence's block table and position + 1"""
+    T, W = batch.tokens.shape[0], batch.block_tables.shape[1]
+    tables = torch.empty((T, W), dtype=torch.int32, device=batch.tokens.device)
+    ctx = torch.empty((T,), dtype=torch.int32, device=batch.tokens.device)
+    lib().token_tables(_ptr(batch.block_tables), C.c_int32(W), _ptr(batch.token_seq), _ptr(batch.positions), _ptr(tables), _ptr(ctx), C.c_int32(T),
+                       _stream(tables.device))
+    check("token_tables")
+    return tables, ctx
+
+
+LATENT_DECODE_WORKSPACE = 1 << 31      # bytes of partials one call of the split-KV kernel may use; steps with more rows go in slabs
+
+
+def latent_attention_decode(q_abs: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor, tables: torch.Tensor, context_lens: torch.Tensor,
                             sink: Optional[torch.Tensor], scale: float) -> torch.Tensor:
-    """A step of single tokens on the split-KV tensor-core kernel of the latent cache (csrc/mla.cu: TMA tiles, 16 heads per MMA, partials folded by a
-    merge kernel that also takes the sink): q_abs bf16 [B, H, 512], q_rot bf16 [B, H, 64], bf16 caches of 64-token blocks -> bf16 [B, H, 512]."""
-    B, H, R = q_abs.shape
-    W = batch.block_tables.shape[1]
+    """Rows as one-row sequences (``token_tables``) on the split-KV tensor-core kernel of the latent cache (csrc/mla.cu: TMA tiles, 16 heads per MMA,
+    runs of 256 keys folded by a merge kernel that also takes the sink): q_abs bf16 [T, H, 512], q_rot bf16 [T, H, 64], bf16 caches of 64-token
+    blocks -> bf16 [T, H, 512].  Serves single decoded tokens and rows of prompts alike (each row has its own context length)."""
+    T, H, R = q_abs.shape
+    W = tables.shape[1]
     bs = c_cache.shape[1]
-    out = torch.empty((B, H, R), dtype=torch.bfloat16, device=q_abs.device)
+    out = torch.empty((T, H, R), dtype=torch.bfloat16, device=q_abs.device)
     L = lib()
-    need = int(L.mla_paged_decode_workspace_bytes(C.c_int32(B), C.c_int32(H), C.c_int32(W), C.c_int32(bs)))
+    per_row = int(L.mla_paged_decode_workspace_bytes(C.c_int32(1), C.c_int32(H), C.c_int32(W), C.c_int32(bs)))
+    slab = max(1, min(T, 65535, LATENT_DECODE_WORKSPACE // per_row))
+    need = int(L.mla_paged_decode_workspace_bytes(C.c_int32(slab), C.c_int32(H), C.c_int32(W), C.c_int32(bs)))
     ws = torch.empty(need, dtype=torch.uint8, device=q_abs.device)
-    L.mla_paged_attention_sink(_ptr(out), _ptr(q_abs), _ptr(q_rot), _ptr(c_cache), _ptr(kr_cache), _ptr(batch.block_tables), _ptr(context_lens), _ptr(None), _ptr(sink),
-                               C.c_int32(B), C.c_int32(B), C.c_int32(H), C.c_int32(R), C.c_int32(q_rot.shape[2]), C.c_int32(bs), C.c_int32(W), C.c_int64(c_cache.shape[0]),
-                               C.c_float(scale), C.c_int32(DType.BF16), _ptr(ws), C.c_size_t(need), _stream(q_abs.device))
-    check("latent_attention_decode")
+    for r0 in range(0, T, slab):
+        n = min(slab, T - r0)
+        L.mla_paged_attention_sink(_ptr(out[r0:]), _ptr(q_abs[r0:]), _ptr(q_rot[r0:]), _ptr(c_cache), _ptr(kr_cache), _ptr(tables[r0:]), _ptr(context_lens[r0:]), _ptr(None),
+                                   _ptr(sink), C.c_int32(n), C.c_int32(n), C.c_int32(H), C.c_int32(R), C.c_int32(q_rot.shape[2]), C.c_int32(bs), C.c_int32(W),
+                                   C.c_int64(c_cache.shape[0]), C.c_float(scale), C.c_int32(DType.BF16), _ptr(ws), C.c_size_t(need), _stream(q_abs.device))
+        check("latent_attention_decode")
     return out

@@ -524,6 +524,10 @@ void latent_out_gate(const float* src, int64_t src_stride_token, int64_t src_str
  *   split-KV decode kernel (mla_decode_kernel_supported(...) == 1, one row per sequence).
  * repack_heads: dst[t, h, :n] (bf16) = src[t, h, :n] (F32 / BF16), both with their own token / head strides (elements); with context_lens (u32 [T]) also
  *   context_lens[t] = positions[t] + 1. */
+/* token_tables: out_tables u32 [T, table_width] = the block table of every row's sequence (block_tables i32 [B, table_width], row token_seq[t]) and
+ *   context_lens[t] = positions[t] + 1: every row as a one-row sequence for mla_paged_attention_sink. */
+void token_tables(const int32_t* block_tables, int32_t table_width, const int32_t* token_seq, const int32_t* positions, uint32_t* out_tables,
+                  uint32_t* context_lens, int32_t num_tokens, int64_t stream);
 int32_t mla_decode_kernel_supported(int32_t kv_lora_rank, int32_t qk_rope_head_dim, int32_t block_size, int32_t dtype);
 void mla_paged_attention_sink(void* out, const void* q_absorbed, const void* q_pe, const void* ckv_cache, const void* kpe_cache, const uint32_t* block_tables,
                               const uint32_t* context_lens, const uint32_t* cu_seqlens_q, const float* sink, int32_t num_seqs, int32_t num_rows, int32_t num_heads,

@@ -483,8 +483,9 @@ def test_many_rows_take_the_tensor_core_routes():
 
 
 def test_single_token_steps_on_the_split_kv_latent_kernel():
-    """latent 512 + rotated 64 in bf16 with 64-token blocks: steps of 16 and more single tokens run on the split-KV tensor-core kernel of the latent
-    cache, whose merge takes the sink; contexts on both sides of its 256-key runs and of block borders, scattered blocks, decoded side by side"""
+    """latent 512 + rotated 64 in bf16 with 64-token blocks: steps of 16 and more rows (single tokens and rows of prompts alike) run on the split-KV
+    tensor-core kernel of the latent cache, whose merge takes the sink; contexts on both sides of its 256-key runs and of block borders, scattered
+    blocks, decoded side by side"""
     cfg = S.guvusun_config(128, 150, [S.guvusun_layer(4, 64, 64, 32, 512, experts=4, ff=64, top=2, identity=1, scaling=YARN),
                                       S.guvusun_layer(3, 64, 64, 40, 512, kv_from=0, scaling=YARN)], bigram=dict(buckets=31, mul_prev=7, mul_cur=3))
     w = S.guvusun_weights(cfg, 5)
@@ -500,7 +501,10 @@ def test_single_token_steps_on_the_split_kv_latent_kernel():
     got = [[] for _ in lens]
     for i in reversed(range(len(lens))):                                                # admitted in reverse: tables are not in sequence order
         runner.admit(i)
-        runner.execute([dict(seq_id=i, tokens=seqs[i][:lens[i]], want=[])])
+        out = runner.execute([dict(seq_id=i, tokens=seqs[i][:lens[i]], want=list(range(lens[i])))])
+        if lens[i] >= 16:                                                               # rows of prompts take the same kernel, each with its own context length
+            e = row_errors(out, refs[i][:lens[i]])
+            assert float(e.median()) < 0.03 and float(e.max()) < 0.3, (i, float(e.median()), float(e.max()))
     for k in range(steps):
         out = runner.execute([dict(seq_id=i, tokens=[seqs[i][lens[i] + k]], want=[0]) for i in range(len(lens))])
         for i in range(len(lens)):
