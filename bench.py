@@ -929,7 +929,7 @@ def run_guvusun(args):
         kern = {}
         names = ["linear", "linear_grouped", "rms_norm_ex", "residual_rms_norm", "embedding_bigram", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb",
                  "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "moe_sorted_rows", "moe_gather_rows", "silu_mul_packed",
-                 "moe_combine_rows", "repack_heads", "latent_attention_decode"]
+                 "moe_combine_rows", "repack_heads", "latent_attention_decode", "token_tables"]
         orig = {n: getattr(ops, n) for n in names}
 
         def instrument(tag):
@@ -1013,6 +1013,9 @@ def run_guvusun(args):
                 # sequence are read once per group of 8 heads
                 "latent_attention_varlen": ("f32", ctx_sum * H * (2 * Wd + 2 * R)) if tag == "prefill" else ("bytes", ctx_sum * Wd * esz),
                 "mla_paged_prefill": ("f32", ctx_sum * H * (2 * Wd + 2 * R)), "mla_paged_decode": ("bytes", ctx_sum * Wd * esz),
+                # rows on the split-KV tensor-core kernel: tensor work for prompts, cache bytes (once per 16 heads) for single tokens
+                "latent_attention_decode": ("flops", ctx_sum * H * (2 * Wd + 2 * R)) if tag == "prefill" else ("bytes", ctx_sum * Wd * esz * -(-H // 16)),
+                "repack_heads": ("bytes", T * H * (R * 6 + R * 4 + dr * 6) / 3), "token_tables": ("bytes", T * (blocks_per + 1) * 8),
                 "moe_route": ("bytes", T * ((E + z["identity"]) * 4 + top * 8)),
                 "moe_gate_up": ("bytes", min(T * top, E) * 2 * ff * D * esz), "moe_down": ("bytes", min(T * top, E) * ff * D * esz),
                 "moe_gather_rows": ("bytes", T * top * D * esz * 2), "silu_mul_packed": ("bytes", T * top * ff * (8 + esz)),
