@@ -72,8 +72,10 @@ struct DenseParams {
     int out_dtype, bf16;
     int ksplit;                    // swap mode, f32 output: the k range is cut into ksplit parts per tile (more CTAs than weight tiles); partial
     int accumulate;                // sums meet in y through fp32 atomics.  accumulate: y += result (f32 output)
-    // grouped form (not swapped): the BN-row operand is a stack of `groups` matrices of group_rows rows each, and tile_group[ta] (device,
-    // written by an earlier kernel) names the one that the 128-row tile ta multiplies; a negative entry marks a tile without rows
+    // grouped form: the weight operand is a stack of `groups` matrices of group_rows rows each, and tile_group[i] (device, written by an
+    // earlier kernel) names the one that activation tile i multiplies; a negative entry marks a tile without rows.  Not swapped: activation
+    // tiles are the 128-row tiles ta.  Swapped (few rows per group): activation tiles are the BN-row tiles tb, the weight tile ta is counted
+    // inside the group, and tiles are walked group by group.
     const int32_t* tile_group;
     int group_rows;
 };
@@ -138,6 +140,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constan
     };
     auto tile_coords = [&](int t, int& ta, int& tb) {
         if (p.ksplit > 1) { ta = t / p.ksplit; tb = 0; return; }
+        if (p.tile_group && p.swap) { tb = t / p.tiles_a; ta = t - tb * p.tiles_a; return; }
         constexpr int kBand = 8;
         const int per_band = kBand * p.tiles_b;
         const int band = t / per_band, r = t - band * per_band;
@@ -157,11 +160,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constan
             int ta, tb, kb0, kb1;
             tile_coords(t, ta, tb);
             k_range(t, kb0, kb1);
-            int brow = tb * kBN;
+            int arow = ta * kBM, brow = tb * kBN;
             if (p.tile_group) {
-                const int g = p.tile_group[ta];
+                const int g = p.tile_group[p.swap ? tb : ta];
                 if (g < 0) continue;                         // all three roles skip the same tiles
-                brow += g * p.group_rows;
+                if (p.swap) arow += g * p.group_rows; else brow += g * p.group_rows;
             }
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int s = it % kS;
@@ -169,7 +172,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constan
                 if (leader) {
                     mbar_expect_tx(full(s), C::kStageBytes);
                     const uint32_t dst = smem_base + s * C::kStageBytes;
-                    tma_load_2d(dst, &amap, full(s), kb * kBK, ta * kBM, pol);
+                    tma_load_2d(dst, &amap, full(s), kb * kBK, arow, pol);
                     tma_load_2d(dst + C::kABytes, &bmap, full(s), kb * kBK, brow, pol);
                 }
                 __syncwarp();
@@ -186,7 +189,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constan
             if (p.tile_group) {
                 int ta, tb;
                 tile_coords(t, ta, tb);
-                if (p.tile_group[ta] < 0) continue;
+                if (p.tile_group[p.swap ? tb : ta] < 0) continue;
             }
             const int ab = tcount & 1;
             mbar_wait(tmem_empty(ab), ((tcount >> 1) & 1) ^ 1);          // the epilogue has drained this accumulator
@@ -224,7 +227,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constan
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
             int ta, tb;
             tile_coords(t, ta, tb);
-            if (p.tile_group && p.tile_group[ta] < 0) continue;
+            if (p.tile_group && p.tile_group[p.swap ? tb : ta] < 0) continue;
             const int ab = tcount & 1;
             mbar_wait(tmem_full(ab), (tcount >> 1) & 1);
             tc_fence_after();
@@ -379,19 +382,27 @@ bool dense_gemm_16(const void* x, const void* w, const void* bias, void* y, int 
     return check_launch("dense_gemm");
 }
 
-// Grouped form: y[r, :n] = x[r, :] . w[g(r)]^T for a stack w [groups, n, k]; the rows of x come in 128-row tiles that each belong to one group,
-// tile_group[i] (device i32 [m_pad / 128]) = the group of tile i or -1 for a tile to skip.  m_pad % 128 == 0.
-bool dense_gemm_grouped_16(const void* x, const void* w, void* y, int m_pad, int n, int k, int groups, const int32_t* tile_group, int64_t ldx, int64_t ldy,
-                           int out_dtype, cudaStream_t st) {
+// Grouped form: y[r, :n] = x[r, :] . w[g(r)]^T for a stack w [groups, n, k]; the rows of x come in tiles of tile_rows that each belong to one group,
+// tile_group[i] (device i32 [m_pad / tile_rows]) = the group of tile i or -1 for a tile to skip.  m_pad % tile_rows == 0.
+bool dense_gemm_grouped_16(const void* x, const void* w, void* y, int m_pad, int n, int k, int groups, const int32_t* tile_group, int tile_rows, int64_t ldx,
+                           int64_t ldy, int out_dtype, cudaStream_t st) {
     if (m_pad <= 0 || n <= 0 || k <= 0 || groups <= 0) return true;
     if (out_dtype != B200_BF16 && out_dtype != B200_F32) { set_error(kErrUnsupported, "dense_gemm_grouped: out dtype %d (f32 / bf16)", out_dtype); return false; }
-    if (m_pad % kBM || k % 8 || ldx % 8 || (((uintptr_t)x | (uintptr_t)w) & 15) || !tile_group) {
-        set_error(kErrBadArg, "dense_gemm_grouped: rows must come in tiles of 128, k and ldx in multiples of 8 elements, x and w 16-byte aligned (TMA)");
+    if ((tile_rows != kBM && tile_rows != 32 && tile_rows != 64) || m_pad % tile_rows || k % 8 || ldx % 8 || (((uintptr_t)x | (uintptr_t)w) & 15) || !tile_group) {
+        set_error(kErrBadArg, "dense_gemm_grouped: rows must come in tiles of 128 (or 32 / 64), k and ldx in multiples of 8 elements, x and w 16-byte aligned (TMA)");
         return false;
     }
     DenseParams p{};
     p.y = y; p.bias = nullptr; p.m = m_pad; p.n = n; p.k = k; p.ldy = ldy; p.out_dtype = out_dtype; p.bf16 = 1;
     p.ksplit = 1; p.accumulate = 0; p.swap = 0; p.tile_group = tile_group; p.group_rows = n;
+    if (tile_rows != kBM) {
+        // few rows per group: the weights are the 128-row operand (every group's weight tiles stream once per activation tile of 32 / 64 rows)
+        p.swap = 1; p.tiles_a = (n + kBM - 1) / kBM; p.tiles_b = m_pad / tile_rows;
+        CUtensorMap am, bm;
+        if (!make_map(&am, w, groups * n, k, k, kBM, true) || !make_map(&bm, x, m_pad, k, ldx, tile_rows, true)) return false;
+        if (tile_rows == 32) launch_out<32>(am, bm, p, st); else launch_out<64>(am, bm, p, st);
+        return check_launch("dense_gemm_grouped");
+    }
     int bn = 256;
     auto tiles = [&](int b) { return (int64_t)(m_pad / kBM) * ((n + b - 1) / b); };
     if (n <= 128 || tiles(256) < sm_count()) bn = 128;
@@ -409,13 +420,14 @@ using namespace b200;
 
 extern "C" {
 
-// linear_grouped: out[r, :n] (f32 or bf16, row pitch ldy) = x[r, :k] . weight[tile_group[r / 128]]^T for bf16 x [m_pad, k] (row pitch ldx) and a bf16
-// stack weight [groups, n, k]; tiles whose entry is negative are skipped (their rows of out stay untouched).
-void linear_grouped(const void* x, const void* weight, void* out, const int32_t* tile_group, int32_t m_pad, int32_t n, int32_t k, int32_t groups, int64_t ldx,
-                    int64_t ldy, int32_t out_dtype, int64_t stream) {
+// linear_grouped: out[r, :n] (f32 or bf16, row pitch ldy) = x[r, :k] . weight[tile_group[r / tile_rows]]^T for bf16 x [m_pad, k] (row pitch ldx) and a bf16
+// stack weight [groups, n, k]; tiles whose entry is negative are skipped (their rows of out stay untouched).  tile_rows = 128, or 32 / 64 for few rows per
+// group (the weights then take the 128-row side of the MMA).
+void linear_grouped(const void* x, const void* weight, void* out, const int32_t* tile_group, int32_t tile_rows, int32_t m_pad, int32_t n, int32_t k, int32_t groups,
+                    int64_t ldx, int64_t ldy, int32_t out_dtype, int64_t stream) {
     if (m_pad == 0 || n == 0) return;
     B200_REQUIRE(x && weight && out && tile_group && m_pad > 0 && n > 0 && k > 0 && groups > 0 && ldx >= k && ldy >= n, kErrBadArg, "linear_grouped: bad arguments");
-    dense_gemm_grouped_16(x, weight, out, m_pad, n, k, groups, tile_group, ldx, ldy, out_dtype, as_stream(stream));
+    dense_gemm_grouped_16(x, weight, out, m_pad, n, k, groups, tile_group, tile_rows, ldx, ldy, out_dtype, as_stream(stream));
 }
 
 // Linear::forward on dense 16-bit weights (linear.rs:124-172): out[m, n] = x[m, k] . weight[n, k]^T (+ bias[n]); x / weight / bias / out of

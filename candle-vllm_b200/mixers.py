@@ -142,7 +142,7 @@ class GatedMlp:
         return ops.linear(ops.gelu_tanh_mul(ops.linear(h, self.w_in), self.dtype), self.w_down)
 
 
-GROUPED_MIN_ROWS = 256        # token-choice pairs from which the grouped tensor-core products replace the streaming expert kernels
+GROUPED_MIN_ROWS = 256        # token-choice pairs from which the expert products take 128-row tiles per expert (below: 32-row tiles, weights on the 128-row side)
 GROUPED_MIN_TOKENS = 16       # rows from which the latent up-projections run head by head on the tensor-core GEMM (each head's rows padded to 128)
 
 
@@ -273,12 +273,15 @@ class RoutedExperts:
     def forward(self, h: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         """h: the input in the compute dtype, x: the same rows in f32 (what an identity expert returns)"""
         ids, wts = ops.moe_route(ops.linear(h, self.router), self.correction, self.top, self.groups, self.keep, self.scale)
-        if self.grouped and h.shape[0] * self.top >= GROUPED_MIN_ROWS:
-            pair_row, row_pair, tile_expert = ops.moe_sorted_rows(ids, self.E)
+        if self.grouped:
+            # pairs sorted by expert into tiles of 128 rows, or of 32 while experts have few rows each (the weights then take the 128-row side of the MMA and
+            # stream once per tile)
+            tile = 128 if h.shape[0] * self.top >= GROUPED_MIN_ROWS else 32
+            pair_row, row_pair, tile_expert = ops.moe_sorted_rows(ids, self.E, tile)
             xg = ops.moe_gather_rows(h, row_pair, self.top)
-            gu = ops.linear_grouped(xg, self.w_gu, tile_expert, torch.empty((xg.shape[0], 2 * self.ff), dtype=torch.float32, device=h.device))
+            gu = ops.linear_grouped(xg, self.w_gu, tile_expert, torch.empty((xg.shape[0], 2 * self.ff), dtype=torch.float32, device=h.device), tile)
             act = ops.silu_mul_packed(gu, torch.bfloat16)
-            y = ops.linear_grouped(act, self.w_d, tile_expert, torch.empty((xg.shape[0], self.w_d.shape[1]), dtype=torch.float32, device=h.device))
+            y = ops.linear_grouped(act, self.w_d, tile_expert, torch.empty((xg.shape[0], self.w_d.shape[1]), dtype=torch.float32, device=h.device), tile)
             return ops.moe_combine_rows(y, pair_row, wts, x)
         if not self.E:                                       # identity experts only
             return ops.moe_combine_rows(x, torch.full((ids.numel(),), -1, dtype=torch.int32, device=ids.device), wts, x)

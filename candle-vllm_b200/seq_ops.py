@@ -338,15 +338,16 @@ def latent_out_gate(src: torch.Tensor, w_uv: Optional[torch.Tensor], gate: Optio
     return out
 
 
-def linear_grouped(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[r, :n] = x[r] . weight[tile_group[r // 128]]^T on the tcgen05 GEMM: x bf16 [m_pad, k] (m_pad % 128 == 0, rows may be strided), weight bf16
-    [groups, n, k], tile_group i32 [m_pad / 128] (negative = skip the tile), out f32 or bf16 [m_pad, >= n] (rows may be strided)."""
+def linear_grouped(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tensor, out: torch.Tensor, tile: int = 128) -> torch.Tensor:
+    """out[r, :n] = x[r] . weight[tile_group[r // tile]]^T on the tcgen05 GEMM: x bf16 [m_pad, k] (m_pad % tile == 0, rows may be strided), weight bf16
+    [groups, n, k], tile_group i32 [m_pad / tile] (negative = skip the tile), out f32 or bf16 [m_pad, >= n] (rows may be strided).  tile = 128, or
+    32 / 64 when groups have few rows (the weights then take the 128-row side of the MMA)."""
     m, k = x.shape
     G, n, _ = weight.shape
-    if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not weight.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1 or m % 128 or
-            tile_group.dtype != torch.int32 or tile_group.numel() < m // 128 or weight.shape[2] != k or out.shape[0] != m or out.shape[1] < n):
+    if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not weight.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1 or m % tile or
+            tile_group.dtype != torch.int32 or tile_group.numel() < m // tile or weight.shape[2] != k or out.shape[0] != m or out.shape[1] < n):
         raise BackendError(f"linear_grouped: x {tuple(x.shape)} {x.dtype}, weight {tuple(weight.shape)} {weight.dtype}, out {tuple(out.shape)}")
-    lib().linear_grouped(_ptr(x), _ptr(weight), _ptr(out), _ptr(tile_group), C.c_int32(m), C.c_int32(n), C.c_int32(k), C.c_int32(G), C.c_int64(x.stride(0)),
+    lib().linear_grouped(_ptr(x), _ptr(weight), _ptr(out), _ptr(tile_group), C.c_int32(tile), C.c_int32(m), C.c_int32(n), C.c_int32(k), C.c_int32(G), C.c_int64(x.stride(0)),
                          C.c_int64(out.stride(0)), C.c_int32(_tag(out.dtype)), _stream(x.device))
     check("linear_grouped")
     return out

@@ -535,17 +535,18 @@ void mla_paged_attention_sink(void* out, const void* q_absorbed, const void* q_p
                               int32_t dtype, void* workspace, size_t workspace_bytes, int64_t stream);
 void repack_heads(const void* src, int32_t src_dtype, int64_t src_stride_token, int64_t src_stride_head, void* dst, int64_t dst_stride_token, int64_t dst_stride_head,
                   int32_t num_tokens, int32_t num_heads, int32_t n, const int32_t* positions, uint32_t* context_lens, int64_t stream);
-/* linear_grouped: out[r, :n] (out_dtype F32 / BF16, row pitch ldy) = x[r, :k] . weight[tile_group[r / 128]]^T: bf16 x [m_pad, k] (row pitch ldx, m_pad a
- *   multiple of 128) whose rows come in tiles of 128 that each multiply one matrix of the bf16 stack weight [groups, n, k]; tile_group i32 [m_pad / 128] on
- *   the device, a negative entry skips the tile.  The tcgen05 GEMM of linear_16bit with the weight tile chosen per row tile.
+/* linear_grouped: out[r, :n] (out_dtype F32 / BF16, row pitch ldy) = x[r, :k] . weight[tile_group[r / tile_rows]]^T: bf16 x [m_pad, k] (row pitch ldx, m_pad a
+ *   multiple of tile_rows) whose rows come in tiles of tile_rows (128; or 32 / 64 when groups have few rows: the weights then take the 128-row side of the
+ *   MMA) that each multiply one matrix of the bf16 stack weight [groups, n, k]; tile_group i32 [m_pad / tile_rows] on the device, a negative entry skips the
+ *   tile.  The tcgen05 GEMM of linear_16bit with the weight tile chosen per row tile.
  * moe_align: pairs (token, choice) sorted by expert into tiles of `tile` rows (128 for linear_grouped; 1 = plain sort): ids i32 [pairs]; pair_row[p] = its
  *   row in the sorted, padded order (-1 for an identity choice, id >= num_experts), row_pair i32 [max_rows] the inverse (-1 = padding), tile_group i32
  *   [max_rows / tile] the expert of every tile (-1 = unused; may be null when tile == 1); max_rows >= moe_align_rows(pairs, num_experts, tile).
  * moe_gather_rows: xg bf16 [max_rows, width] = h[row_pair[r] / top] (zeros for padding).
  * silu_mul_packed: out[r, :ff] = silu(gu[r, :ff]) * gu[r, ff : 2 ff] from f32 gu, out_dtype F32 / BF16.
  * moe_combine_rows: out f32 [T, width] = sum_k weights[t, k] * (pair_row >= 0 ? y[pair_row[t, k]] : x[t]), in choice order. */
-void linear_grouped(const void* x, const void* weight, void* out, const int32_t* tile_group, int32_t m_pad, int32_t n, int32_t k, int32_t groups, int64_t ldx,
-                    int64_t ldy, int32_t out_dtype, int64_t stream);
+void linear_grouped(const void* x, const void* weight, void* out, const int32_t* tile_group, int32_t tile_rows, int32_t m_pad, int32_t n, int32_t k, int32_t groups,
+                    int64_t ldx, int64_t ldy, int32_t out_dtype, int64_t stream);
 int64_t moe_align_rows(int64_t pairs, int32_t num_experts, int32_t tile);
 void moe_align(const int32_t* ids, int32_t* pair_row, int32_t* row_pair, int32_t* tile_group, int32_t pairs, int32_t num_experts, int32_t max_rows, int32_t tile,
                int64_t stream);

@@ -167,20 +167,21 @@ def test_routed_experts(E, I, top, ff, D, groups, dtype, tol):
     close(mlp.forward(dev(x, dtype), dev(x)), G.moe(x.to(F64), w, cfg["layers"][0]["mlp"]), tol, "routed experts")
 
 
+@pytest.mark.parametrize("tile", [128, 32, 64])
 @pytest.mark.parametrize("n,k,G", [(64, 64, 3), (40, 72, 5), (300, 128, 2), (24, 200, 4)])
-def test_grouped_product_on_the_tensor_core_gemm(n, k, G):
-    """rows in tiles of 128, every tile multiplying the matrix its entry names (in any order, with skipped tiles), against float64 on the
-    same bf16 operands; rows of skipped tiles stay as they were"""
+def test_grouped_product_on_the_tensor_core_gemm(n, k, G, tile):
+    """rows in tiles of 128 (or 32 / 64: the form for few rows per matrix, weights on the 128-row side of the MMA), every tile multiplying the
+    matrix its entry names (in any order, with skipped tiles), against float64 on the same bf16 operands; rows of skipped tiles stay as they were"""
     g = torch.Generator().manual_seed(n + k)
     tiles = [1, -1, 0, G - 1, 1, -1, 0]
-    m = 128 * len(tiles)
+    m = tile * len(tiles)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16)
     w = (torch.randn(G, n, k, generator=g) * k ** -0.5).to(torch.bfloat16)
     for dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 6e-3)):
         out = torch.full((m, n + 8), 3.0, dtype=dt, device=DEV)
-        ops.linear_grouped(x.to(DEV), w.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV), out)
+        ops.linear_grouped(x.to(DEV), w.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV), out, tile)
         for i, e in enumerate(tiles):
-            rows = slice(128 * i, 128 * i + 128)
+            rows = slice(tile * i, tile * i + tile)
             if e < 0:
                 assert float((out[rows].float() - 3.0).abs().max()) == 0.0
             else:
@@ -193,17 +194,18 @@ def test_pairs_sorted_by_expert():
     E, T, top = 5, 333, 3
     ids = torch.randint(0, E + 2, (T, top), generator=g).to(torch.int32)           # ids E, E + 1 are identity choices
     ids[ids == 3] = 4                                                              # an expert nobody chose
-    pair_row, row_pair, tile_group = (t.cpu() for t in ops.moe_sorted_rows(ids.to(DEV), E))
     flat = ids.reshape(-1)
-    assert row_pair.shape[0] % 128 == 0 and tile_group.shape[0] == row_pair.shape[0] // 128
-    for p in range(T * top):
-        r = int(pair_row[p])
-        if flat[p] >= E:
-            assert r == -1
-        else:
-            assert int(row_pair[r]) == p and int(tile_group[r // 128]) == int(flat[p])
-    assert int((row_pair >= 0).sum()) == int((flat < E).sum())
-    assert 3 not in tile_group.tolist()
+    for tile in (128, 32, 1):
+        pair_row, row_pair, tile_group = (t.cpu() for t in ops.moe_sorted_rows(ids.to(DEV), E, tile))
+        assert row_pair.shape[0] % tile == 0 and tile_group.shape[0] == row_pair.shape[0] // tile
+        for p in range(T * top):
+            r = int(pair_row[p])
+            if flat[p] >= E:
+                assert r == -1
+            else:
+                assert int(row_pair[r]) == p and int(tile_group[r // tile]) == int(flat[p])
+        assert int((row_pair >= 0).sum()) == int((flat < E).sum())
+        assert 3 not in tile_group.tolist()
 
 
 def _mixer_case(H, dn, dr, dv, R, D, scaling, seed=0, **kw):
