@@ -999,6 +999,8 @@ def run_guvusun(args):
             if key.startswith("linear_grouped["):
                 gcount, n, k = (int(v) for v in key[15:-1].split("x"))
                 rows = T * top if gcount == E else T * H
+                if tag == "decode":                 # few rows per matrix: every matrix that has rows streams once (all of them, as an upper bound)
+                    return ("bytes", min(rows, gcount) * n * k * esz)
                 return ("flops", 2.0 * rows * n * k)
             ctx_sum = T * (T + 1) / 2 if tag == "prefill" else T * (CTX + 1)
             return {
